@@ -10,8 +10,10 @@ own storage, page pool and page table, so runs with different needs never share 
 
 A sequence lives in a *slot* from its first token to its end and holds, in each group, the
 pages its length needs; a group with a window gives pages back as soon as they lie wholly
-before the window.  A run that reads another run's cache (``cache_of``) gets a view of that
-run's plane and writes nothing.  Runs that ask for fixed-size state get one tensor
+before the window, except the pages of the first ``keep_first`` positions when the request asks to
+keep those.  A run that reads another run's cache (``cache_of``) gets a view of that
+run's plane and writes nothing; what the owner's group keeps is then the union of what the owner
+and its readers see (the widest window, the most kept first positions).  Runs that ask for fixed-size state get one tensor
 ``[slots, ...]`` each, zeroed when a slot is opened (the reference keeps recurrent state of
 this kind in its run state, include/model_run_state.h:21-23, zeroed on reset,
 src/session.c:145-167).  The reference's own key/value arrays are per session and
@@ -19,7 +21,7 @@ src/session.c:145-167).  The reference's own key/value arrays are per session an
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -98,6 +100,7 @@ class KvGroup:
         if self.request.window > 0:
             # the oldest key any new token needs: position old_len - window + 1
             first = max(0, old_len - self.request.window + 1) // PAGE
+        # (with ``keep_first`` the first pages were taken when the sequence began and are never given back)
         need = [i for i in range(first, pages_for(new_len)) if i not in held]
         if need and need[-1] >= self.pages_per_seq:
             raise CacheFull(f"a sequence of {new_len} tokens needs page {need[-1]}, "
@@ -115,7 +118,8 @@ class KvGroup:
             return
         held = self.held.get(slot, {})
         first_needed = max(0, length - self.request.window + 1) // PAGE
-        gone = [i for i in held if i < first_needed]
+        kept = pages_for(self.request.keep_first)  # the pages of the first positions stay
+        gone = [i for i in held if kept <= i < first_needed]
         self.pool.free([held.pop(i) for i in gone])
 
     def release(self, slot: int) -> None:
@@ -150,6 +154,15 @@ class Cache:
         pages_per_seq = min(pages_for(max_positions), n_pages)
         self.groups: List[KvGroup] = []
         self._plane: Dict[int, Tuple[int, int]] = {}  # schedule entry -> (group, plane)
+        # a run that reads another's plane may look further back than the owner does: the owner's plane
+        # keeps whatever any of them sees
+        kv_requests = list(kv_requests)
+        for i, src in enumerate(cache_of):
+            a = kv_requests[i] if src is not None else None
+            b = kv_requests[src] if src is not None and 0 <= src < len(kv_requests) else None
+            if a is not None and b is not None:
+                window = 0 if (a.window <= 0 or b.window <= 0) else max(a.window, b.window)
+                kv_requests[src] = replace(b, window=window, keep_first=max(a.keep_first, b.keep_first))
         by_request: Dict[KvRequest, List[int]] = {}
         for i, req in enumerate(kv_requests):
             if req is not None and cache_of[i] is None:

@@ -1,4 +1,5 @@
 """Typed configuration, the block-by-block model description, and the architecture registry."""
+from .spec import (BiasAttentionSpec, MlstmSpec, MoeSpec, PostNormBlockSpec)  # noqa: F401
 from .spec import (AttentionSpec, BlockSpec, ConfigError, GatedMlpSpec, LinearHeadSpec, ModelSpec, NoPositionSpec,
                    RmsNormSpec, RotarySpec, ScheduleEntry)
 from .registry import (Architecture, architecture, architecture_of, known_architectures,
@@ -15,9 +16,22 @@ register_architecture(Architecture(
     config_to_dict=LlamaConfig.to_dict,
 ))
 
+from . import fesorax as _fesorax
+from .fesorax import FesoraxConfig
+
+register_architecture(Architecture(
+    name=_fesorax.ARCHITECTURE,
+    read_config=FesoraxConfig.from_dict,
+    to_spec=FesoraxConfig.to_spec,
+    tensor_name=_fesorax.tensor_name,
+    cap_positions=FesoraxConfig.with_max_positions,
+    config_to_dict=FesoraxConfig.to_dict,
+    complete_config=_fesorax.with_sizes_of,
+))
+
 __all__ = [
     "AttentionSpec", "BlockSpec", "ConfigError", "GatedMlpSpec", "LinearHeadSpec", "ModelSpec", "NoPositionSpec",
     "RmsNormSpec", "RotarySpec", "ScheduleEntry", "Architecture", "architecture", "architecture_of",
     "known_architectures", "read_config_json", "register_architecture", "unregister_architecture",
-    "LlamaConfig",
+    "LlamaConfig", "FesoraxConfig", "BiasAttentionSpec", "MlstmSpec", "MoeSpec", "PostNormBlockSpec",
 ]

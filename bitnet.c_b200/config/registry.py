@@ -2,7 +2,7 @@
 
 The reference walks a table of ``BnModelArchOps`` and takes the first entry whose
 predicate matches the GGUF architecture string (src/model_arch.c:862-987).  Here
-the key is ``config.json``'s ``architectures[0]`` and an unknown name is an error
+the key is ``config.json``'s ``architectures[0]`` (or its ``architecture`` string) and an unknown name is an error
 that lists the known ones.
 """
 from __future__ import annotations
@@ -31,6 +31,9 @@ class Architecture:
     tensor_name: Callable[[str], str]
     cap_positions: Callable[[Any, int], Any]
     config_to_dict: Callable[[Any], Dict[str, Any]]
+    # optional: ``complete_config(dict, shapes)`` fills in sizes that only the file's tensors fix
+    # (``shapes``: tensor name -> shape) before the configuration is read
+    complete_config: Any = None
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
@@ -74,7 +77,10 @@ def read_config_json(model_dir: str) -> Dict[str, Any]:
 
 def architecture_of(config_dict: Dict[str, Any]) -> Architecture:
     archs = config_dict.get("architectures")
-    if not archs or not isinstance(archs, (list, tuple)) or not isinstance(archs[0], str):
-        raise ConfigError("config.json has no 'architectures' list; known: "
-                          + ", ".join(known_architectures()))
-    return architecture(archs[0])
+    if isinstance(archs, (list, tuple)) and archs and isinstance(archs[0], str):
+        return architecture(archs[0])
+    one = config_dict.get("architecture")  # some files name their one architecture by a plain string
+    if isinstance(one, str) and one:
+        return architecture(one)
+    raise ConfigError("config.json has no 'architectures' list and no 'architecture' name; known: "
+                      + ", ".join(known_architectures()))

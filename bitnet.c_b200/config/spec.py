@@ -26,6 +26,7 @@ class RmsNormSpec:
     width: int
     eps: float
     kind: str = "rmsnorm"
+    optional: bool = False  # the file may lack the gain; the norm is then not applied by who owns it
 
 
 @dataclass(frozen=True)
@@ -76,6 +77,61 @@ class AttentionSpec:
 
 
 @dataclass(frozen=True)
+class BiasAttentionSpec:
+    """Causal softmax attention with grouped key/value heads in its general form: value heads of a width
+    of their own, queries and keys optionally divided by their root mean square per head, an optional
+    learned bias by log-bucketed distance, a window that may keep the first tokens, an optional logistic
+    gate per head on the output, and keys and values that may be another run's."""
+
+    width: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    v_head_dim: int
+    scale: float
+    window: int = 0  # 0: every earlier key; w > 0: the last w keys ...
+    keep_first: int = 0  # ... and the keys at positions below this
+    unit_norm: bool = False  # q and k divided by their root mean square over the head (eps: norm_eps)
+    norm_eps: float = 1e-6
+    bias_buckets: int = 0  # rows of the distance-bias table; 0: no bias
+    bias_max_distance: int = 0  # the distance from which on the last bucket is used
+    head_gate: bool = False  # one gate per head from the mixer's input
+    own_kv: bool = True  # False: no key/value projections; the run reads another run's cache
+    kind: str = "bias_attention"
+
+
+@dataclass(frozen=True)
+class MlstmSpec:
+    """mLSTM: a matrix memory per head with exponential gating, a soft cap on the gates' pre-activations,
+    a unit norm per head, a gain over all heads and a logistic output gate."""
+
+    width: int
+    n_heads: int
+    head_dim: int
+    v_head_dim: int
+    gate_cap: float
+    norm_eps: float
+    kind: str = "mlstm"
+
+
+@dataclass(frozen=True)
+class MoeSpec:
+    """Mixture of clamped gated experts with logistic router scores, optionally with a shared expert."""
+
+    width: int
+    n_experts: int
+    top: int
+    expert_ff: int
+    expert_limit: float
+    shared_ff: int = 0  # 0: no shared expert
+    shared_limit: float = 0.0
+    slope: float = 1.702  # the activation is g * sigmoid(slope * g) * (u + 1)
+    weight_on_input: bool = True  # the router weight multiplies the expert's input (False: its output)
+    renormalise: bool = False  # divide the chosen experts' weights by their sum
+    kind: str = "moe"
+
+
+@dataclass(frozen=True)
 class GatedMlpSpec:
     """Dense feed-forward ``down(act(gate x) * up x)``."""
 
@@ -94,6 +150,19 @@ class BlockSpec:
     mixer_norm: Any
     ffn_norm: Any
     kind: str = "pre_norm"
+
+
+@dataclass(frozen=True)
+class PostNormBlockSpec:
+    """A block whose norms follow the sums: x <- norm(alpha x + mixer(x)), x <- norm(alpha x + ffn(x)).
+    ``ffn`` may be None (no feed-forward); ``ffn_norm`` is then applied to alpha x if it is given."""
+
+    mixer: Any
+    ffn: Any
+    mixer_norm: Any
+    ffn_norm: Any
+    alpha: float = 1.0
+    kind: str = "post_norm"
 
 
 @dataclass(frozen=True)

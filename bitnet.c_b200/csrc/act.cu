@@ -81,3 +81,35 @@ extern "C" int bn_scale_softcap(float* x, long long n, float scale, float cap, c
   BN_LAUNCH(scale_softcap_kernel, blocks, 256, 0, stream, x, (size_t)n, scale, cap);
   return BN_OK;
 }
+
+// Clamped gated unit: rows of h hold `inter` gate values and then `inter` up values;
+// g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(slope * g) * (u + 1).
+template <typename T>
+__global__ void glu_limited_kernel(const T* __restrict__ h, T* __restrict__ out, int inter, size_t total, float limit,
+                                   float slope) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  size_t t = idx / inter;
+  size_t j = idx - t * inter;
+  float g = fminf(to_f32<T>(h[t * 2 * inter + j]), limit);
+  float u = fminf(fmaxf(to_f32<T>(h[t * 2 * inter + inter + j]), -limit), limit);
+  out[idx] = from_f32<T>(g / (1.0f + expf(-slope * g)) * (u + 1.0f));
+}
+
+extern "C" int bn_glu_limited(const void* h, void* out, int dtype, int n_rows, int inter, float limit, float slope,
+                              cudaStream_t stream) {
+  if (n_rows <= 0) return BN_OK;
+  if (inter <= 0 || !h || !out) return BN_ERR_BAD_ARG;
+  size_t total = (size_t)n_rows * inter;
+  unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == BN_F32)
+    BN_LAUNCH(glu_limited_kernel<float>, blocks, 256, 0, stream, (const float*)h, (float*)out, inter, total, limit, slope);
+  else if (dtype == BN_BF16)
+    BN_LAUNCH(glu_limited_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)h, (__nv_bfloat16*)out,
+              inter, total, limit, slope);
+  else
+    return BN_ERR_BAD_ARG;
+  return BN_OK;
+}

@@ -38,10 +38,19 @@ struct Vec16<__nv_bfloat16> {
   }
 };
 
+// Optional extras, each off when its pointer is null or its number zero, so that one kernel
+// serves every softmax attention of the library:
+//   v_dim        width of a value head when it differs from a key head's
+//   keep_first   with a window: keys at positions below keep_first stay visible however far back
+//   rel, n_rel   additive bias by distance, rel[min(pos - p, n_rel - 1) * n_heads + h] (float32; the
+//                scale does not multiply it)
+//   gate         per token and head a number whose logistic function multiplies the head's output
 template <typename T>
 __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out,
-                                         int out_stride, int n_heads, int n_kv_heads, int head_dim,
-                                         float scale, int window, const int* __restrict__ tok_seq,
+                                         int out_stride, int n_heads, int n_kv_heads, int head_dim, int v_dim,
+                                         float scale, int window, int keep_first, const float* __restrict__ rel,
+                                         int n_rel, const T* __restrict__ gate, int gate_stride,
+                                         const int* __restrict__ tok_seq,
                                          const int* __restrict__ tok_pos, const int* __restrict__ slots,
                                          const int* __restrict__ page_table, int pt_stride,
                                          const T* __restrict__ k_cache, const T* __restrict__ v_cache) {
@@ -56,21 +65,25 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
   int pos = tok_pos[t];
   const int* pt = page_table + (size_t)slots[tok_seq[t]] * pt_stride;
   int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  // visible keys: positions [0, n_first) and [lo, pos]; u counts through both ranges
+  int n_first = min(keep_first, lo);
+  int n_keys = n_first + pos - lo + 1;
 
   const T* qrow = q + (size_t)t * q_stride + (size_t)h * head_dim;
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) qs[d] = to_f32<T>(qrow[d]);
   __syncthreads();
 
   constexpr int VN = Vec16<T>::N;
-  constexpr int MAX_D = 2;  // output dims per thread: head_dim <= 256
+  constexpr int MAX_D = 2;  // output dims per thread: v_dim <= 256
   float acc[MAX_D] = {0.f, 0.f};
   float m_run = -INFINITY, l_run = 0.f;
 
-  for (int base = lo; base <= pos; base += ATT_CHUNK) {
-    int n = min(ATT_CHUNK, pos - base + 1);
+  for (int base = 0; base < n_keys; base += ATT_CHUNK) {
+    int n = min(ATT_CHUNK, n_keys - base);
     float s = -INFINITY;
     if ((int)threadIdx.x < n) {
-      int p = base + threadIdx.x;
+      int u = base + threadIdx.x;
+      int p = u < n_first ? u : lo + (u - n_first);
       const T* krow = k_cache + cache_row_offset(pt, p, n_kv_heads, kvh, head_dim);
       float dot = 0.f;
       for (int d = 0; d < head_dim; d += VN) {
@@ -80,6 +93,7 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
         for (int e = 0; e < VN; ++e) dot = fmaf(qs[d + e], kv[e], dot);
       }
       s = dot * scale;
+      if (rel) s += rel[(size_t)min(pos - p, n_rel - 1) * n_heads + h];
     }
     float m_chunk = block_max(s, scratch);
     float m_new = fmaxf(m_run, m_chunk);
@@ -92,10 +106,12 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
 #pragma unroll
     for (int r = 0; r < MAX_D; ++r) {
       int d = threadIdx.x + r * ATT_THREADS;
-      if (d < head_dim) {
+      if (d < v_dim) {
         float a = acc[r] * alpha;
         for (int j = 0; j < n; ++j) {
-          const T* vrow = v_cache + cache_row_offset(pt, base + j, n_kv_heads, kvh, head_dim);
+          int u = base + j;
+          int p = u < n_first ? u : lo + (u - n_first);
+          const T* vrow = v_cache + cache_row_offset(pt, p, n_kv_heads, kvh, v_dim);
           a = fmaf(ps[j], to_f32<T>(vrow[d]), a);
         }
         acc[r] = a;
@@ -104,39 +120,53 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
     __syncthreads();  // ps[] is rewritten by the next chunk
   }
   float inv = 1.0f / l_run;
-  T* orow = out + (size_t)t * out_stride + (size_t)h * head_dim;
+  if (gate) inv *= 1.0f / (1.0f + expf(-to_f32<T>(gate[(size_t)t * gate_stride + h])));
+  T* orow = out + (size_t)t * out_stride + (size_t)h * v_dim;
 #pragma unroll
   for (int r = 0; r < MAX_D; ++r) {
     int d = threadIdx.x + r * ATT_THREADS;
-    if (d < head_dim) orow[d] = from_f32<T>(acc[r] * inv);
+    if (d < v_dim) orow[d] = from_f32<T>(acc[r] * inv);
   }
 }
 
-// q: [n_tokens, q_stride] with head h at element h*head_dim; out likewise with out_stride.
-// The keys and values of the new tokens must already be in the cache.
-extern "C" int bn_attention_general(const void* q, int q_stride, void* out, int out_stride, int dtype,
-                                    int n_tokens, int n_heads, int n_kv_heads, int head_dim, float scale,
-                                    int window, const int* tok_seq, const int* tok_pos, const int* slots,
-                                    const int* page_table, int pt_stride,
-                                    const void* k_cache, const void* v_cache, cudaStream_t stream) {
+// q: [n_tokens, q_stride] with head h at element h*head_dim; out [n_tokens, out_stride] with head h at
+// element h*v_dim.  The keys and values of the new tokens must already be in the cache.
+extern "C" int bn_attention_general_ex(const void* q, int q_stride, void* out, int out_stride, int dtype,
+                                       int n_tokens, int n_heads, int n_kv_heads, int head_dim, int v_dim, float scale,
+                                       int window, int keep_first, const float* rel, int n_rel, const void* gate,
+                                       int gate_stride, const int* tok_seq, const int* tok_pos, const int* slots,
+                                       const int* page_table, int pt_stride,
+                                       const void* k_cache, const void* v_cache, cudaStream_t stream) {
   if (n_tokens <= 0) return BN_OK;
   if (head_dim <= 0 || head_dim % 16 || head_dim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads ||
-      window < 0)
+      window < 0 || keep_first < 0 || v_dim <= 0 || v_dim > 256 || (rel && n_rel <= 0))
     return BN_ERR_BAD_ARG;
   if (n_heads > 65535) return BN_ERR_BAD_ARG;
   dim3 grid(n_tokens, n_heads);
   size_t smem = (head_dim + ATT_CHUNK + 32) * sizeof(float);
   if (dtype == BN_F32)
     BN_LAUNCH((attention_general_kernel<float>), grid, ATT_THREADS, smem, stream, 
-        (const float*)q, q_stride, (float*)out, out_stride, n_heads, n_kv_heads, head_dim, scale, window,
+        (const float*)q, q_stride, (float*)out, out_stride, n_heads, n_kv_heads, head_dim, v_dim, scale, window,
+        keep_first, rel, n_rel, (const float*)gate, gate_stride,
         tok_seq, tok_pos, slots, page_table, pt_stride, (const float*)k_cache, (const float*)v_cache);
   else if (dtype == BN_BF16)
     BN_LAUNCH((attention_general_kernel<__nv_bfloat16>), grid, ATT_THREADS, smem, stream, 
-        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, head_dim,
-        scale, window, tok_seq, tok_pos, slots, page_table, pt_stride,
+        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, head_dim, v_dim,
+        scale, window, keep_first, rel, n_rel, (const __nv_bfloat16*)gate, gate_stride,
+        tok_seq, tok_pos, slots, page_table, pt_stride,
         (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache);
   else
     return BN_ERR_BAD_ARG;
   BN_CHECK_LAUNCH();
   return BN_OK;
+}
+
+extern "C" int bn_attention_general(const void* q, int q_stride, void* out, int out_stride, int dtype,
+                                    int n_tokens, int n_heads, int n_kv_heads, int head_dim, float scale,
+                                    int window, const int* tok_seq, const int* tok_pos, const int* slots,
+                                    const int* page_table, int pt_stride,
+                                    const void* k_cache, const void* v_cache, cudaStream_t stream) {
+  return bn_attention_general_ex(q, q_stride, out, out_stride, dtype, n_tokens, n_heads, n_kv_heads, head_dim, head_dim,
+                                 scale, window, 0, nullptr, 0, nullptr, 0, tok_seq, tok_pos, slots, page_table,
+                                 pt_stride, k_cache, v_cache, stream);
 }

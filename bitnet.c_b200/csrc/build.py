@@ -44,6 +44,9 @@ SOURCES: Dict[str, str] = {
     "gemm_tc": "gemm_tc.cu",
     "sampling": "sampling.cu",
     "argmax_noalloc": "argmax_noalloc.cu",
+    "unit_norm": "unit_norm.cu",
+    "mlstm": "mlstm.cu",
+    "moe": "moe.cu",
 }
 
 NVCC_FLAGS = [

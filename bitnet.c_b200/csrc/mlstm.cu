@@ -1,0 +1,204 @@
+// mLSTM: a matrix memory per head with exponential input gate and a stabiliser.
+//
+// Per head, with log input gate i_t, log forget gate f_t (both float32), keys k_t and queries q_t of
+// `dim` numbers (the query already scaled) and values v_t of `vdim` numbers:
+//
+//   m_t = max(f_t + m_{t-1}, i_t)
+//   a = exp(f_t + m_{t-1} - m_t),  b = exp(i_t - m_t)
+//   S_t = a S_{t-1} + b k_t v_t^T          [dim, vdim]
+//   n_t = a n_{t-1} + b k_t                [dim]
+//   o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + 1e-6)
+//
+// S, n and m start at zero for a new sequence and live in float32 in the state manager's tensor
+//   state[slot][head] = { S[dim][vdim], n[dim], m }
+// from step to step.  The three kernels here:
+//   bn_mlstm_gates       i, f from the mixer's input (a float32 product with 2 * heads rows) with their soft cap
+//   bn_mlstm_recurrence  the recurrence over the new tokens of every sequence, token by token
+//   bn_mlstm_output      per head o / rms(o), times a gain over all heads, times the logistic output gate
+#include "common.cuh"
+
+#define ML_GATE_THREADS 128
+
+// gates[t][0..H) = cap * tanh((W_i h + b_i) / cap);  gates[t][H..2H) = logsigmoid(cap * tanh((W_f h + b_f) / cap))
+// w: [2H, width] (input gate rows first), bias: [2H].
+template <typename T, typename W>
+__global__ void mlstm_gates_kernel(const T* __restrict__ h, int width, const W* __restrict__ w,
+                                   const W* __restrict__ bias, int n_heads, float cap, float* __restrict__ gates) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  const T* row = h + (size_t)t * width;
+  for (int r = warp; r < 2 * n_heads; r += n_warps) {
+    const W* wr = w + (size_t)r * width;
+    float dot = 0.f;
+    for (int c = lane; c < width; c += 32) dot = fmaf(to_f32<T>(row[c]), to_f32<W>(wr[c]), dot);
+    dot = warp_sum(dot);
+    if (lane == 0) {
+      float z = cap * tanhf((dot + to_f32<W>(bias[r])) / cap);
+      if (r >= n_heads) z = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));  // log(sigmoid(z))
+      gates[(size_t)t * 2 * n_heads + r] = z;
+    }
+  }
+}
+
+extern "C" int bn_mlstm_gates(const void* h, int h_dtype, int n_tokens, int width, const void* w, const void* bias,
+                              int w_dtype, int n_heads, float cap, float* gates, cudaStream_t stream) {
+  if (n_tokens <= 0) return BN_OK;
+  if (!h || !w || !bias || !gates || width <= 0 || n_heads <= 0 || !(cap > 0.f)) return BN_ERR_BAD_ARG;
+  if (h_dtype == BN_F32 && w_dtype == BN_F32)
+    BN_LAUNCH((mlstm_gates_kernel<float, float>), n_tokens, ML_GATE_THREADS, 0, stream, (const float*)h, width,
+              (const float*)w, (const float*)bias, n_heads, cap, gates);
+  else if (h_dtype == BN_BF16 && w_dtype == BN_BF16)
+    BN_LAUNCH((mlstm_gates_kernel<__nv_bfloat16, __nv_bfloat16>), n_tokens, ML_GATE_THREADS, 0, stream,
+              (const __nv_bfloat16*)h, width, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, n_heads, cap, gates);
+  else if (h_dtype == BN_BF16 && w_dtype == BN_F32)
+    BN_LAUNCH((mlstm_gates_kernel<__nv_bfloat16, float>), n_tokens, ML_GATE_THREADS, 0, stream,
+              (const __nv_bfloat16*)h, width, (const float*)w, (const float*)bias, n_heads, cap, gates);
+  else
+    return BN_ERR_BAD_ARG;
+  BN_CHECK_LAUNCH();
+  return BN_OK;
+}
+
+// One block per (sequence, head, chunk of value columns); thread c owns column c0 + c of S, which
+// lies in shared memory as S[d][c].  Every block of a head keeps n and m itself (the same numbers
+// in the same order in each), the block of chunk 0 writes them back.
+template <typename T>
+__global__ void mlstm_recurrence_kernel(const T* __restrict__ qkv, int row_stride, int k_off, int v_off,
+                                        const float* __restrict__ gates, float* __restrict__ state,
+                                        const int* __restrict__ seq_start, const int* __restrict__ slots, int n_heads,
+                                        int dim, int vdim, int cols, float q_scale, float* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  float* S = sm;                   // dim * cols
+  float* sq = S + (size_t)dim * cols;  // dim
+  float* sk = sq + dim;            // dim
+  float* sn = sk + dim;            // dim
+  const int seq = blockIdx.x, head = blockIdx.y, c0 = blockIdx.z * cols;
+  const int c = threadIdx.x, lane = threadIdx.x & 31;
+  const bool has_col = c < cols && c0 + c < vdim;
+  const size_t per_head = (size_t)dim * vdim + dim + 1;
+  float* st = state + ((size_t)slots[seq] * n_heads + head) * per_head;
+  float* st_n = st + (size_t)dim * vdim;
+  if (has_col)
+    for (int d = 0; d < dim; ++d) S[d * cols + c] = st[(size_t)d * vdim + c0 + c];
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) sn[d] = st_n[d];
+  float m = st_n[dim];
+  const int t0 = seq_start[seq], t1 = seq_start[seq + 1];
+  for (int t = t0; t < t1; ++t) {
+    const T* row = qkv + (size_t)t * row_stride;
+    __syncthreads();  // the step before has read sq, sk
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+      sq[d] = to_f32<T>(row[(size_t)head * dim + d]) * q_scale;
+      sk[d] = to_f32<T>(row[k_off + (size_t)head * dim + d]);
+    }
+    float gi = gates[(size_t)t * 2 * n_heads + head], gf = gates[(size_t)t * 2 * n_heads + n_heads + head];
+    float m_new = fmaxf(gf + m, gi);
+    float a = expf(gf + m - m_new), b = expf(gi - m_new);
+    m = m_new;
+    __syncthreads();
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) sn[d] = a * sn[d] + b * sk[d];
+    __syncthreads();
+    float nq = 0.f;
+    for (int d = lane; d < dim; d += 32) nq = fmaf(sn[d], sq[d], nq);
+    nq = warp_sum(nq);
+    float denom = fmaxf(fabsf(nq), expf(-m)) + 1e-6f;
+    if (has_col) {
+      float v = to_f32<T>(row[v_off + (size_t)head * vdim + c0 + c]);
+      float bv = b * v, acc = 0.f;
+      for (int d = 0; d < dim; ++d) {
+        float s = fmaf(a, S[d * cols + c], bv * sk[d]);
+        S[d * cols + c] = s;
+        acc = fmaf(s, sq[d], acc);
+      }
+      out[(size_t)t * n_heads * vdim + (size_t)head * vdim + c0 + c] = acc / denom;
+    }
+  }
+  if (has_col)
+    for (int d = 0; d < dim; ++d) st[(size_t)d * vdim + c0 + c] = S[d * cols + c];
+  __syncthreads();
+  if (blockIdx.z == 0) {
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) st_n[d] = sn[d];
+    if (threadIdx.x == 0) st_n[dim] = m;
+  }
+}
+
+// qkv: rows of the new tokens with the query heads at element 0, key heads at k_off, value heads at
+// v_off; gates [n_tokens, 2 * heads]; state [slots, heads, dim * vdim + dim + 1]; out [n_tokens, heads * vdim] float32.
+extern "C" int bn_mlstm_recurrence(const void* qkv, int dtype, int row_stride, int k_off, int v_off, const float* gates,
+                                   float* state, const int* seq_start, const int* slots, int n_seqs, int n_heads, int dim,
+                                   int vdim, float q_scale, float* out, cudaStream_t stream) {
+  if (n_seqs <= 0) return BN_OK;
+  if (!qkv || !gates || !state || !out || n_heads <= 0 || dim <= 0 || vdim <= 0 || n_heads > 65535) return BN_ERR_BAD_ARG;
+  int cols = vdim >= 128 ? 128 : (vdim + 31) / 32 * 32;
+  while (cols > 32 && ((size_t)dim * cols + 3 * dim) * sizeof(float) > 160 * 1024) cols /= 2;
+  size_t smem = ((size_t)dim * cols + 3 * (size_t)dim) * sizeof(float);
+  if (smem > 200 * 1024) return BN_ERR_BAD_ARG;
+  int chunks = (vdim + cols - 1) / cols;
+  if (chunks > 65535) return BN_ERR_BAD_ARG;
+  dim3 grid(n_seqs, n_heads, chunks);
+  static size_t granted_f = 0, granted_b = 0;
+  if (dtype == BN_F32) {
+    if (smem > 48 * 1024 && smem > granted_f) {
+      cudaError_t e = cudaFuncSetAttribute(mlstm_recurrence_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
+      granted_f = smem;
+    }
+    BN_LAUNCH(mlstm_recurrence_kernel<float>, grid, cols, smem, stream, (const float*)qkv, row_stride, k_off, v_off, gates,
+              state, seq_start, slots, n_heads, dim, vdim, cols, q_scale, out);
+  } else if (dtype == BN_BF16) {
+    if (smem > 48 * 1024 && smem > granted_b) {
+      cudaError_t e = cudaFuncSetAttribute(mlstm_recurrence_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
+      granted_b = smem;
+    }
+    BN_LAUNCH(mlstm_recurrence_kernel<__nv_bfloat16>, grid, cols, smem, stream, (const __nv_bfloat16*)qkv, row_stride,
+              k_off, v_off, gates, state, seq_start, slots, n_heads, dim, vdim, cols, q_scale, out);
+  } else {
+    return BN_ERR_BAD_ARG;
+  }
+  BN_CHECK_LAUNCH();
+  return BN_OK;
+}
+
+// out[t][h][c] = o[t][h][c] / sqrt(mean_c(o[t][h]^2) + eps) * gain[h * vdim + c] * sigmoid(g[t][h * vdim + c])
+template <typename T, typename W>
+__global__ void mlstm_output_kernel(const float* __restrict__ o, const W* __restrict__ gain, const T* __restrict__ g,
+                                    int g_stride, int n_heads, int vdim, float eps, T* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  for (int h = warp; h < n_heads; h += n_warps) {
+    const float* oh = o + ((size_t)t * n_heads + h) * vdim;
+    float ss = 0.f;
+    for (int c = lane; c < vdim; c += 32) ss = fmaf(oh[c], oh[c], ss);
+    ss = warp_sum(ss);
+    float scale = 1.0f / sqrtf(ss / (float)vdim + eps);
+    for (int c = lane; c < vdim; c += 32) {
+      float gate = 1.0f / (1.0f + expf(-to_f32<T>(g[(size_t)t * g_stride + (size_t)h * vdim + c])));
+      out[((size_t)t * n_heads + h) * vdim + c] = from_f32<T>(oh[c] * scale * to_f32<W>(gain[(size_t)h * vdim + c]) * gate);
+    }
+  }
+}
+
+extern "C" int bn_mlstm_output(const float* o, const void* gain, int gain_dtype, const void* g, int g_stride, int dtype,
+                               int n_tokens, int n_heads, int vdim, float eps, void* out, cudaStream_t stream) {
+  if (n_tokens <= 0) return BN_OK;
+  if (!o || !gain || !g || !out || n_heads <= 0 || vdim <= 0 || !(eps > 0.f)) return BN_ERR_BAD_ARG;
+  if (dtype == BN_F32 && gain_dtype == BN_F32)
+    BN_LAUNCH((mlstm_output_kernel<float, float>), n_tokens, 128, 0, stream, o, (const float*)gain, (const float*)g,
+              g_stride, n_heads, vdim, eps, (float*)out);
+  else if (dtype == BN_BF16 && gain_dtype == BN_BF16)
+    BN_LAUNCH((mlstm_output_kernel<__nv_bfloat16, __nv_bfloat16>), n_tokens, 128, 0, stream, o, (const __nv_bfloat16*)gain,
+              (const __nv_bfloat16*)g, g_stride, n_heads, vdim, eps, (__nv_bfloat16*)out);
+  else if (dtype == BN_BF16 && gain_dtype == BN_F32)
+    BN_LAUNCH((mlstm_output_kernel<__nv_bfloat16, float>), n_tokens, 128, 0, stream, o, (const float*)gain,
+              (const __nv_bfloat16*)g, g_stride, n_heads, vdim, eps, (__nv_bfloat16*)out);
+  else
+    return BN_ERR_BAD_ARG;
+  BN_CHECK_LAUNCH();
+  return BN_OK;
+}

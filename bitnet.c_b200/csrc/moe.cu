@@ -1,0 +1,299 @@
+// Mixture of experts with sigmoid scores: routing, and the expert products for few tokens.
+//
+//   z = W_router h (float32), s = sigmoid(z); each token takes the `top` experts with the largest
+//   scores; its weight for an expert is that expert's score, taken as it is (or renormalised over the
+//   chosen ones), and multiplies either the expert's input or its output.
+//
+//   bn_moe_route     ids[t][k], weights[t][k] for every token
+//   bn_moe_gate_up   y[t * top + k] = act(W_gate[e] x, W_up[e] x) with x = h[t] (times the weight, when it
+//                    scales the input) for e = ids[t][k]
+//   bn_moe_down      out[t] = sum_k (weight) W_down[e] y[t * top + k] (+ what a shared expert gave), float32
+//   bn_moe_scale_rows  x[t * top + k] = weight[t][k] * h[t], for the path that multiplies expert by expert
+//
+// The two product kernels stream an expert's matrices once per (token, expert) and are meant for the
+// few rows of a decode step; they read everything they need from device memory, so a step that
+// uses them can be recorded.  With many rows the tokens are sorted by expert instead and every
+// expert's rows go through the library's ordinary products (parts/moe.py).
+//
+// The activation is the clamped gated unit of act.cu: g = min(gate, limit), u = clamp(up, +-limit),
+// y = g * sigmoid(slope * g) * (u + 1).
+#include "common.cuh"
+
+#define MOE_MAX_EXPERTS 1024
+
+template <typename T, typename W>
+__global__ void moe_route_kernel(const T* __restrict__ h, int width, const W* __restrict__ w, int n_experts, int top,
+                                 int renormalise, int* __restrict__ ids, float* __restrict__ weights) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float z[MOE_MAX_EXPERTS];
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  const T* row = h + (size_t)t * width;
+  for (int e = warp; e < n_experts; e += n_warps) {
+    const W* wr = w + (size_t)e * width;
+    float dot = 0.f;
+    for (int c = lane; c < width; c += 32) dot = fmaf(to_f32<T>(row[c]), to_f32<W>(wr[c]), dot);
+    dot = warp_sum(dot);
+    if (lane == 0) z[e] = dot;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+      // the largest logit left; among equal ones the lowest index
+      float best = -INFINITY;
+      int arg = n_experts;
+      for (int e = lane; e < n_experts; e += 32)
+        if (z[e] > best) { best = z[e]; arg = e; }
+      for (int o = 16; o > 0; o >>= 1) {
+        float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+        if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+      }
+      float s = 1.0f / (1.0f + expf(-best));
+      total += s;
+      if (lane == 0) {
+        ids[(size_t)t * top + k] = arg;
+        weights[(size_t)t * top + k] = s;
+        z[arg] = -INFINITY;
+      }
+      __syncwarp();
+    }
+    if (renormalise && lane < top) weights[(size_t)t * top + lane] /= total;
+  }
+}
+
+extern "C" int bn_moe_route(const void* h, int h_dtype, int n_tokens, int width, const void* w, int w_dtype,
+                            int n_experts, int top, int renormalise, int* ids, float* weights, cudaStream_t stream) {
+  if (n_tokens <= 0) return BN_OK;
+  if (!h || !w || !ids || !weights || width <= 0 || n_experts <= 0 || n_experts > MOE_MAX_EXPERTS || top <= 0 ||
+      top > n_experts || top > 32)
+    return BN_ERR_BAD_ARG;
+  if (h_dtype == BN_F32 && w_dtype == BN_F32)
+    BN_LAUNCH((moe_route_kernel<float, float>), n_tokens, 128, 0, stream, (const float*)h, width, (const float*)w,
+              n_experts, top, renormalise, ids, weights);
+  else if (h_dtype == BN_BF16 && w_dtype == BN_BF16)
+    BN_LAUNCH((moe_route_kernel<__nv_bfloat16, __nv_bfloat16>), n_tokens, 128, 0, stream, (const __nv_bfloat16*)h, width,
+              (const __nv_bfloat16*)w, n_experts, top, renormalise, ids, weights);
+  else if (h_dtype == BN_BF16 && w_dtype == BN_F32)
+    BN_LAUNCH((moe_route_kernel<__nv_bfloat16, float>), n_tokens, 128, 0, stream, (const __nv_bfloat16*)h, width,
+              (const float*)w, n_experts, top, renormalise, ids, weights);
+  else
+    return BN_ERR_BAD_ARG;
+  BN_CHECK_LAUNCH();
+  return BN_OK;
+}
+
+#define MOE_THREADS 256
+#define MOE_ROWS_PER_BLOCK 32  // outputs per block of the product kernels
+
+// grid (tokens * top, ceil(ff / MOE_ROWS_PER_BLOCK)); row j of expert e's gate matrix lies at
+// w_gate + e * expert_stride + j * width, of its up matrix at w_up + the same (so that one tensor
+// [experts, 2 * ff, width] with the gate rows first serves both)
+template <typename T>
+__global__ void moe_gate_up_kernel(const T* __restrict__ h, int width, const int* __restrict__ ids,
+                                   const float* __restrict__ weights, int scale_input, const T* __restrict__ w_gate,
+                                   const T* __restrict__ w_up, size_t expert_stride, int ff, int top, float limit,
+                                   float slope, T* __restrict__ y) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float xs[];  // width
+  const int item = blockIdx.x, t = item / top;
+  const int e = ids[item];
+  const float wt = scale_input ? weights[item] : 1.0f;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  // the expert's input in the compute type, as the path that sorts tokens by expert stores it
+  for (int c = threadIdx.x; c < width; c += blockDim.x)
+    xs[c] = to_f32<T>(from_f32<T>(to_f32<T>(h[(size_t)t * width + c]) * wt));
+  __syncthreads();
+  const int j0 = blockIdx.y * MOE_ROWS_PER_BLOCK, j1 = min(ff, j0 + MOE_ROWS_PER_BLOCK);
+  for (int j = j0 + warp; j < j1; j += n_warps) {
+    const T* gr = w_gate + (size_t)e * expert_stride + (size_t)j * width;
+    const T* ur = w_up + (size_t)e * expert_stride + (size_t)j * width;
+    float g = 0.f, u = 0.f;
+    for (int c = lane; c < width; c += 32) {
+      g = fmaf(xs[c], to_f32<T>(gr[c]), g);
+      u = fmaf(xs[c], to_f32<T>(ur[c]), u);
+    }
+    g = warp_sum(g);
+    u = warp_sum(u);
+    if (lane == 0) {
+      // the products' results pass through the compute type, as they do on the sorted path
+      g = fminf(to_f32<T>(from_f32<T>(g)), limit);
+      u = fminf(fmaxf(to_f32<T>(from_f32<T>(u)), -limit), limit);
+      y[(size_t)item * ff + j] = from_f32<T>(g / (1.0f + expf(-slope * g)) * (u + 1.0f));
+    }
+  }
+}
+
+// grid (tokens, ceil(width / MOE_ROWS_PER_BLOCK)); w_down: [experts, width, ff]
+template <typename T>
+__global__ void moe_down_kernel(const T* __restrict__ y, int ff, const int* __restrict__ ids,
+                                const float* __restrict__ weights, int scale_output, const T* __restrict__ w_down,
+                                int width, int top, const void* __restrict__ add, int add_dtype, float* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  const int c0 = blockIdx.y * MOE_ROWS_PER_BLOCK, c1 = min(width, c0 + MOE_ROWS_PER_BLOCK);
+  for (int c = c0 + warp; c < c1; c += n_warps) {
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int e = ids[(size_t)t * top + k];
+      const T* wr = w_down + ((size_t)e * width + c) * ff;
+      const T* yr = y + ((size_t)t * top + k) * ff;
+      float dot = 0.f;
+      for (int j = lane; j < ff; j += 32) dot = fmaf(to_f32<T>(yr[j]), to_f32<T>(wr[j]), dot);
+      dot = warp_sum(dot);
+      total += scale_output ? dot * weights[(size_t)t * top + k] : dot;
+    }
+    if (lane == 0) {
+      if (add) total += load_as_f32(add, add_dtype, (size_t)t * width + c);
+      out[(size_t)t * width + c] = total;
+    }
+  }
+}
+
+extern "C" int bn_moe_gate_up(const void* h, int dtype, int n_tokens, int width, const int* ids, const float* weights,
+                              int scale_input, const void* w_gate, const void* w_up, long long expert_stride, int ff, int top,
+                              float limit, float slope, void* y, cudaStream_t stream) {
+  if (n_tokens <= 0) return BN_OK;
+  if (!h || !ids || !weights || !w_gate || !w_up || !y || width <= 0 || ff <= 0 || top <= 0) return BN_ERR_BAD_ARG;
+  size_t smem = (size_t)width * sizeof(float);
+  if (smem > 48 * 1024) return BN_ERR_BAD_ARG;
+  dim3 grid(n_tokens * top, (ff + MOE_ROWS_PER_BLOCK - 1) / MOE_ROWS_PER_BLOCK);
+  if (dtype == BN_F32)
+    BN_LAUNCH(moe_gate_up_kernel<float>, grid, MOE_THREADS, smem, stream, (const float*)h, width, ids, weights, scale_input,
+              (const float*)w_gate, (const float*)w_up, (size_t)expert_stride, ff, top, limit, slope, (float*)y);
+  else if (dtype == BN_BF16)
+    BN_LAUNCH(moe_gate_up_kernel<__nv_bfloat16>, grid, MOE_THREADS, smem, stream, (const __nv_bfloat16*)h, width, ids,
+              weights, scale_input, (const __nv_bfloat16*)w_gate, (const __nv_bfloat16*)w_up, (size_t)expert_stride, ff, top, limit,
+              slope, (__nv_bfloat16*)y);
+  else
+    return BN_ERR_BAD_ARG;
+  BN_CHECK_LAUNCH();
+  return BN_OK;
+}
+
+extern "C" int bn_moe_down(const void* y, int dtype, int n_tokens, int ff, const int* ids, const float* weights,
+                           int scale_output, const void* w_down, int width, int top, const void* add, int add_dtype,
+                           float* out, cudaStream_t stream) {
+  if (n_tokens <= 0) return BN_OK;
+  if (!y || !ids || !weights || !w_down || !out || width <= 0 || ff <= 0 || top <= 0) return BN_ERR_BAD_ARG;
+  dim3 grid(n_tokens, (width + MOE_ROWS_PER_BLOCK - 1) / MOE_ROWS_PER_BLOCK);
+  if (dtype == BN_F32)
+    BN_LAUNCH(moe_down_kernel<float>, grid, MOE_THREADS, 0, stream, (const float*)y, ff, ids, weights, scale_output,
+              (const float*)w_down, width, top, add, add_dtype, out);
+  else if (dtype == BN_BF16)
+    BN_LAUNCH(moe_down_kernel<__nv_bfloat16>, grid, MOE_THREADS, 0, stream, (const __nv_bfloat16*)y, ff, ids, weights,
+              scale_output, (const __nv_bfloat16*)w_down, width, top, add, add_dtype, out);
+  else
+    return BN_ERR_BAD_ARG;
+  BN_CHECK_LAUNCH();
+  return BN_OK;
+}
+
+// ---- sorting tokens by expert (many rows) --------------------------------------------------------
+// counts[e] = how many (token, k) items chose expert e; one thread per item.
+__global__ void moe_count_kernel(const int* __restrict__ ids, int n_items, int* __restrict__ counts) {
+  pdl_launch_dependents();
+  pdl_wait();
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_items) atomicAdd(&counts[ids[i]], 1);
+}
+
+// offsets[e] = first row of expert e in the sorted order (offsets[n_experts] = n_items); one block.
+__global__ void moe_offsets_kernel(const int* __restrict__ counts, int n_experts, int* __restrict__ offsets,
+                                   int* __restrict__ cursor) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < n_experts; ++e) {
+      offsets[e] = at;
+      cursor[e] = at;
+      at += counts[e];
+    }
+    offsets[n_experts] = at;
+  }
+}
+
+// place[i] = row of item i in the sorted order, and x_sorted[place[i]] = weight * h[token of i] (or h itself).
+// Rows of one expert come in any order; every row is computed alone, so the order changes no result.
+template <typename T>
+__global__ void moe_scatter_kernel(const T* __restrict__ h, int width, const int* __restrict__ ids,
+                                   const float* __restrict__ weights, int scale_input, int top, int* __restrict__ cursor,
+                                   int* __restrict__ place, T* __restrict__ x_sorted) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ int row;
+  const int item = blockIdx.x, t = item / top;
+  if (threadIdx.x == 0) {
+    row = atomicAdd(&cursor[ids[item]], 1);
+    place[item] = row;
+  }
+  __syncthreads();
+  const float wt = scale_input ? weights[item] : 1.0f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x)
+    x_sorted[(size_t)row * width + c] = from_f32<T>(to_f32<T>(h[(size_t)t * width + c]) * wt);
+}
+
+// out[t] = sum_k (weight) y_sorted[place[t * top + k]] (+ add[t]), float32
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ y_sorted, int width, const int* __restrict__ place,
+                                  const float* __restrict__ weights, int scale_output, int top,
+                                  const void* __restrict__ add, int add_dtype, float* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+      float v = to_f32<T>(y_sorted[(size_t)place[(size_t)t * top + k] * width + c]);
+      total += scale_output ? v * weights[(size_t)t * top + k] : v;
+    }
+    if (add) total += load_as_f32(add, add_dtype, (size_t)t * width + c);
+    out[(size_t)t * width + c] = total;
+  }
+}
+
+// counts: [n_experts] zeroed by the caller; offsets: [n_experts + 1]; cursor: [n_experts]; place: [n_items]
+extern "C" int bn_moe_sort(const void* h, int dtype, int n_tokens, int width, const int* ids, const float* weights,
+                           int scale_input, int top, int n_experts, int* counts, int* offsets, int* cursor, int* place,
+                           void* x_sorted, cudaStream_t stream) {
+  if (n_tokens <= 0) return BN_OK;
+  if (!h || !ids || !weights || !counts || !offsets || !cursor || !place || !x_sorted || width <= 0 || top <= 0 ||
+      n_experts <= 0)
+    return BN_ERR_BAD_ARG;
+  int n_items = n_tokens * top;
+  BN_LAUNCH(moe_count_kernel, (n_items + 255) / 256, 256, 0, stream, ids, n_items, counts);
+  BN_LAUNCH(moe_offsets_kernel, 1, 32, 0, stream, (const int*)counts, n_experts, offsets, cursor);
+  if (dtype == BN_F32)
+    BN_LAUNCH(moe_scatter_kernel<float>, n_items, 128, 0, stream, (const float*)h, width, ids, weights, scale_input, top,
+              cursor, place, (float*)x_sorted);
+  else if (dtype == BN_BF16)
+    BN_LAUNCH(moe_scatter_kernel<__nv_bfloat16>, n_items, 128, 0, stream, (const __nv_bfloat16*)h, width, ids, weights,
+              scale_input, top, cursor, place, (__nv_bfloat16*)x_sorted);
+  else
+    return BN_ERR_BAD_ARG;
+  BN_CHECK_LAUNCH();
+  return BN_OK;
+}
+
+extern "C" int bn_moe_gather(const void* y_sorted, int dtype, int n_tokens, int width, const int* place,
+                             const float* weights, int scale_output, int top, const void* add, int add_dtype, float* out,
+                             cudaStream_t stream) {
+  if (n_tokens <= 0) return BN_OK;
+  if (!y_sorted || !place || !weights || !out || width <= 0 || top <= 0) return BN_ERR_BAD_ARG;
+  if (dtype == BN_F32)
+    BN_LAUNCH(moe_gather_kernel<float>, n_tokens, 256, 0, stream, (const float*)y_sorted, width, place, weights,
+              scale_output, top, add, add_dtype, out);
+  else if (dtype == BN_BF16)
+    BN_LAUNCH(moe_gather_kernel<__nv_bfloat16>, n_tokens, 256, 0, stream, (const __nv_bfloat16*)y_sorted, width, place,
+              weights, scale_output, top, add, add_dtype, out);
+  else
+    return BN_ERR_BAD_ARG;
+  BN_CHECK_LAUNCH();
+  return BN_OK;
+}

@@ -182,3 +182,53 @@ extern "C" int bn_add_rmsnorm(float* x, const void* delta, int delta_dtype, int 
   BN_CHECK_LAUNCH();
   return BN_OK;
 }
+
+// Norm after the sum (post-norm blocks): v = alpha * x + delta, x = v * rsqrt(mean(v^2) + eps) * w.
+// The float32 residual x is rewritten in place with the norm's output, and `out` (optional)
+// receives the same values in the compute type for the products that read them next.
+__global__ void scaled_add_rmsnorm_kernel(float* __restrict__ x, float alpha, const void* __restrict__ delta,
+                                          int delta_dtype, const void* __restrict__ w, int w_dtype,
+                                          void* __restrict__ out, int out_dtype, int width, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float v[];  // width floats, then 32 for the reduction
+  float* scratch = v + width;
+  size_t row = blockIdx.x;
+  float* xr = x + row * width;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float a = alpha * xr[i];
+    if (delta) a += load_as_f32(delta, delta_dtype, row * width + i);
+    v[i] = a;
+    ss += a * a;
+  }
+  ss = block_sum(ss, scratch);
+  float scale = 1.0f / sqrtf(ss / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float y = v[i] * scale * load_as_f32(w, w_dtype, i);
+    xr[i] = y;
+    if (out) store_from_f32(out, out_dtype, row * width + i, y);
+  }
+}
+
+extern "C" int bn_scaled_add_rmsnorm(float* x, float alpha, const void* delta, int delta_dtype, const void* w,
+                                     int w_dtype, void* out, int out_dtype, int n_rows, int width, float eps,
+                                     cudaStream_t stream) {
+  if (n_rows <= 0) return BN_OK;
+  if (width <= 0 || !(eps > 0.f) || !x || !w) return BN_ERR_BAD_ARG;
+  size_t smem = ((size_t)width + 32) * sizeof(float);
+  if (smem > 200 * 1024) return BN_ERR_BAD_ARG;
+  if (smem > 48 * 1024) {
+    static size_t granted = 0;
+    if (smem > granted) {
+      cudaError_t e = cudaFuncSetAttribute(scaled_add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
+      granted = smem;
+    }
+  }
+  int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  BN_LAUNCH(scaled_add_rmsnorm_kernel, n_rows, threads, smem, stream, x, alpha, delta, delta_dtype, w, w_dtype, out,
+            out_dtype, width, eps);
+  BN_CHECK_LAUNCH();
+  return BN_OK;
+}

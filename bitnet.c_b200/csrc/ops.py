@@ -153,6 +153,30 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
     return out
 
 
+def scaled_add_rmsnorm(x: torch.Tensor, alpha: float, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                       out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """The norm after the sum: x = rmsnorm(alpha * x + delta) * weight, in place on the float32 residual;
+    ``out`` (optional, any float type) receives the same rows for the products that read them next."""
+    _need(x, "x", torch.float32, 2)
+    _need(weight, "weight", dims=1)
+    width = x.shape[1]
+    if weight.shape[0] != width:
+        raise KernelError(f"widths differ: x {width}, weight {weight.shape[0]}")
+    if delta is not None:
+        _need(delta, "delta", dims=2)
+        if tuple(delta.shape) != tuple(x.shape):
+            raise KernelError(f"delta {tuple(delta.shape)} does not match x {tuple(x.shape)}")
+    if out is not None:
+        _need(out, "out", dims=2)
+        if tuple(out.shape) != tuple(x.shape):
+            raise KernelError(f"out {tuple(out.shape)} does not match x {tuple(x.shape)}")
+    _check(_fn("norm", "bn_scaled_add_rmsnorm")(_ptr(x), c_float(alpha), _ptr(delta), int(_code(delta) if delta is not None else 0),
+                                                _ptr(weight), int(_code(weight)), _ptr(out),
+                                                int(_code(out) if out is not None else 0), int(x.shape[0]), int(width),
+                                                c_float(eps), _stream()), "scaled_add_rmsnorm")
+    return out
+
+
 # ---- activation ---------------------------------------------------------------------------
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """Stack gate and up rows as alternating blocks of 8 rows: [g0..g7, u0..u7, g8..g15, u8..u15, ...]."""
@@ -172,6 +196,19 @@ def silu_mul(h: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         raise KernelError(f"silu_mul: h {tuple(h.shape)} and out {tuple(out.shape)} do not fit")
     _check(_fn("act", "bn_silu_mul")(_ptr(h), _ptr(out), int(_code(h)), int(h.shape[0]), int(inter),
                                      _stream()), "silu_mul")
+    return out
+
+
+def glu_limited(h: torch.Tensor, out: torch.Tensor, limit: float, slope: float) -> torch.Tensor:
+    """Rows of h hold ``inter`` gate values and then ``inter`` up values: g = min(gate, limit),
+    u = clamp(up, -limit, limit), out = g * sigmoid(slope * g) * (u + 1)."""
+    _need(h, "h", dims=2)
+    _need(out, "out", h.dtype, 2)
+    inter = h.shape[1] // 2
+    if h.shape[1] != 2 * inter or tuple(out.shape) != (h.shape[0], inter):
+        raise KernelError(f"glu_limited: h {tuple(h.shape)} and out {tuple(out.shape)} do not fit")
+    _check(_fn("act", "bn_glu_limited")(_ptr(h), _ptr(out), int(_code(h)), int(h.shape[0]), int(inter), c_float(limit),
+                                        c_float(slope), _stream()), "glu_limited")
     return out
 
 
@@ -215,12 +252,52 @@ def rope_append(x: torch.Tensor, n_rot_heads: int, head_dim: int, rotary_dims: i
                                          _stream()), "rope_append")
 
 
+def unit_norm_append(x: torch.Tensor, n_q_heads: int, head_dim: int, eps: float, tok_pos: torch.Tensor, *,
+                     k_off: int = 0, v_off: int = 0, n_kv_heads: int = 0, tok_seq: Optional[torch.Tensor] = None,
+                     slots: Optional[torch.Tensor] = None, page_table: Optional[torch.Tensor] = None,
+                     k_cache: Optional[torch.Tensor] = None, v_cache: Optional[torch.Tensor] = None) -> None:
+    """Divide each of the first ``n_q_heads`` heads of every row of x by its root mean square, in
+    place; when a cache is given, do the same to the key heads at ``k_off`` and write them, and the
+    value heads at ``v_off`` as they are, into it (a value head has the width of ``v_cache``'s rows)."""
+    _need(x, "x", dims=2)
+    _need(tok_pos, "tok_pos", torch.int32, 1)
+    n = tok_pos.shape[0]
+    if x.shape[0] < n or n_q_heads * head_dim > x.shape[1]:
+        raise KernelError("unit_norm_append: x is too small for the heads and tokens given")
+    pt_stride, v_dim = 0, 0
+    if k_cache is not None:
+        for t, nm in ((tok_seq, "tok_seq"), (slots, "slots")):
+            _need(t, nm, torch.int32, 1)
+        _need(page_table, "page_table", torch.int32, 2)
+        _need(k_cache, "k_cache", x.dtype, 4)
+        _need(v_cache, "v_cache", x.dtype, 4)
+        v_dim = v_cache.shape[3]
+        if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or tuple(k_cache.shape[:3]) != tuple(v_cache.shape[:3]):
+            raise KernelError(f"unit_norm_append: cache {tuple(k_cache.shape)} / {tuple(v_cache.shape)} does not fit")
+        if k_off + n_kv_heads * head_dim > x.shape[1] or v_off + n_kv_heads * v_dim > x.shape[1]:
+            raise KernelError("unit_norm_append: key/value offsets run past the row")
+        pt_stride = page_table.shape[1]
+    _check(_fn("unit_norm", "bn_unit_norm_append")(_ptr(x), int(_code(x)), int(n), int(x.shape[1]), int(n_q_heads),
+                                                   int(head_dim), c_float(eps), int(k_off), int(v_off), int(n_kv_heads),
+                                                   int(v_dim), _ptr(tok_seq), _ptr(tok_pos), _ptr(slots), _ptr(page_table),
+                                                   int(pt_stride), _ptr(k_cache), _ptr(v_cache), _stream()),
+           "unit_norm_append")
+
+
 # ---- attention ----------------------------------------------------------------------------
 def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_tokens: int, n_heads: int,
                       n_kv_heads: int, head_dim: int, scale: float, window: int, tok_seq: torch.Tensor,
                       tok_pos: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
-                      k_cache: torch.Tensor, v_cache: torch.Tensor) -> torch.Tensor:
-    """Causal attention of every new token over its sequence's pages; q may be a view into a wider row."""
+                      k_cache: torch.Tensor, v_cache: torch.Tensor, *, keep_first: int = 0,
+                      rel: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                      gate_stride: int = 0) -> torch.Tensor:
+    """Causal attention of every new token over its sequence's pages; q may be a view into a wider row.
+
+    A value head may have another width than a key head (the width of ``v_cache``'s rows).  With a
+    window, keys at positions below ``keep_first`` stay visible.  ``rel`` ``[distances, n_heads]``
+    float32 is added to the scaled scores by distance (the last row serves every longer distance).
+    ``gate`` (a view with unit inner stride, row stride ``gate_stride``) holds one number per token and
+    head whose logistic function multiplies the head's output."""
     if not q.is_cuda or q.stride(-1) != 1:
         raise KernelError("attention: q must be a CUDA tensor with unit inner stride")
     _need(out, "out", q.dtype, 2)
@@ -229,14 +306,32 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
     _need(page_table, "page_table", torch.int32, 2)
     _need(k_cache, "k_cache", q.dtype, 4)
     _need(v_cache, "v_cache", q.dtype, 4)
-    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or k_cache.shape != v_cache.shape:
-        raise KernelError(f"attention: cache {tuple(k_cache.shape)} is not [pages, {n_kv_heads}, {PAGE}, {head_dim}]")
-    if head_dim % 16 or head_dim > 256:
-        raise KernelError(f"attention: head_dim={head_dim} must be a multiple of 16 up to 256")
+    v_dim = v_cache.shape[3]
+    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or tuple(k_cache.shape[:3]) != tuple(v_cache.shape[:3]):
+        raise KernelError(f"attention: cache {tuple(k_cache.shape)} / {tuple(v_cache.shape)} is not "
+                          f"[pages, {n_kv_heads}, {PAGE}, {head_dim} / value width]")
+    if head_dim % 16 or head_dim > 256 or v_dim > 256:
+        raise KernelError(f"attention: head_dim={head_dim} must be a multiple of 16 up to 256, value width {v_dim} at most 256")
     if n_heads % n_kv_heads:
         raise KernelError(f"attention: {n_heads} heads are not a multiple of {n_kv_heads} key/value heads")
-    if out.shape[0] < n_tokens or out.shape[1] != n_heads * head_dim:
+    if out.shape[0] < n_tokens or out.shape[1] != n_heads * v_dim:
         raise KernelError("attention: out does not fit")
+    n_rel = 0
+    if rel is not None:
+        _need(rel, "rel", torch.float32, 2)
+        if rel.shape[1] != n_heads or rel.shape[0] < 1:
+            raise KernelError(f"attention: bias table {tuple(rel.shape)} is not [distances, {n_heads}]")
+        n_rel = rel.shape[0]
+    if gate is not None:
+        if not gate.is_cuda or gate.dtype != q.dtype or gate.stride(-1) != 1 or gate.shape[-1] < n_heads or gate_stride <= 0:
+            raise KernelError("attention: gate must be a CUDA view of q's type with unit inner stride and one number per head")
+    if (keep_first or rel is not None or gate is not None or v_dim != head_dim):
+        _check(_fn("attention", "bn_attention_general_ex")(
+            _ptr(q), int(q_stride), _ptr(out), int(out.shape[1]), int(_code(q)), int(n_tokens), int(n_heads),
+            int(n_kv_heads), int(head_dim), int(v_dim), c_float(scale), int(window), int(keep_first), _ptr(rel), int(n_rel),
+            _ptr(gate), int(gate_stride), _ptr(tok_seq), _ptr(tok_pos), _ptr(slots), _ptr(page_table),
+            int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), _stream()), "attention_general")
+        return out
     _check(_fn("attention", "bn_attention_general")(
         _ptr(q), int(q_stride), _ptr(out), int(out.shape[1]), int(_code(q)), int(n_tokens), int(n_heads),
         int(n_kv_heads), int(head_dim), c_float(scale), int(window), _ptr(tok_seq), _ptr(tok_pos),
@@ -874,6 +969,162 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: 
     if swiglu:
         act = torch.empty((M, N // 2), dtype=out.dtype, device=x.device)
         return silu_mul(out, act)
+    return out
+
+
+# ---- mLSTM ----------------------------------------------------------------------------------
+def mlstm_gates(h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor, n_heads: int, cap: float) -> torch.Tensor:
+    """float32 ``[T, 2 * heads]``: per head the soft-capped log input gate, then the log forget gate
+    (the logarithm of the logistic function of the soft-capped pre-activation).  ``w`` ``[2 * heads, width]``
+    holds the input gate's rows first, ``bias`` ``[2 * heads]`` likewise."""
+    _need(h, "h", dims=2)
+    _need(w, "w", dims=2)
+    _need(bias, "bias", w.dtype, 1)
+    if w.shape != (2 * n_heads, h.shape[1]) or bias.shape[0] != 2 * n_heads:
+        raise KernelError(f"mlstm_gates: w {tuple(w.shape)} / bias {tuple(bias.shape)} do not fit {n_heads} heads of width {h.shape[1]}")
+    gates = torch.empty((h.shape[0], 2 * n_heads), dtype=torch.float32, device=h.device)
+    _check(_fn("mlstm", "bn_mlstm_gates")(_ptr(h), int(_code(h)), int(h.shape[0]), int(h.shape[1]), _ptr(w), _ptr(bias),
+                                          int(_code(w)), int(n_heads), c_float(cap), _ptr(gates), _stream()), "mlstm_gates")
+    return gates
+
+
+def mlstm_state_floats(dim: int, vdim: int) -> int:
+    """Floats of one head's state: the matrix ``[dim, vdim]``, the normaliser ``[dim]`` and the stabiliser."""
+    return dim * vdim + dim + 1
+
+
+def mlstm_recurrence(qkv: torch.Tensor, k_off: int, v_off: int, gates: torch.Tensor, state: torch.Tensor,
+                     seq_start: torch.Tensor, slots: torch.Tensor, n_seqs: int, n_heads: int, dim: int, vdim: int,
+                     q_scale: float) -> torch.Tensor:
+    """The matrix-memory recurrence over the new tokens of every sequence, from and into ``state``
+    ``[slots, heads, mlstm_state_floats]`` (float32); returns the heads' raw outputs, float32
+    ``[T, heads * vdim]``.  Rows of ``qkv`` hold the query heads first, key heads at ``k_off``, value heads
+    at ``v_off``."""
+    _need(qkv, "qkv", dims=2)
+    _need(gates, "gates", torch.float32, 2)
+    _need(state, "state", torch.float32, 3)
+    _need(seq_start, "seq_start", torch.int32, 1)
+    _need(slots, "slots", torch.int32, 1)
+    T = qkv.shape[0]
+    if (state.shape[1] != n_heads or state.shape[2] != mlstm_state_floats(dim, vdim) or gates.shape != (T, 2 * n_heads)
+            or max(n_heads * dim, k_off + n_heads * dim, v_off + n_heads * vdim) > qkv.shape[1]
+            or seq_start.shape[0] < n_seqs + 1 or slots.shape[0] < n_seqs):
+        raise KernelError("mlstm_recurrence: sizes do not fit")
+    out = torch.empty((T, n_heads * vdim), dtype=torch.float32, device=qkv.device)
+    _check(_fn("mlstm", "bn_mlstm_recurrence")(_ptr(qkv), int(_code(qkv)), int(qkv.shape[1]), int(k_off), int(v_off),
+                                               _ptr(gates), _ptr(state), _ptr(seq_start), _ptr(slots), int(n_seqs),
+                                               int(n_heads), int(dim), int(vdim), c_float(q_scale), _ptr(out), _stream()),
+           "mlstm_recurrence")
+    return out
+
+
+def mlstm_output(o: torch.Tensor, gain: torch.Tensor, g: torch.Tensor, g_stride: int, n_heads: int, vdim: int, eps: float,
+                 dtype: torch.dtype) -> torch.Tensor:
+    """Per head o / rms(o), times ``gain`` (over all heads), times the logistic function of ``g`` (a view
+    ``[T, heads * vdim]`` with row stride ``g_stride``); result in ``dtype``."""
+    _need(o, "o", torch.float32, 2)
+    _need(gain, "gain", dims=1)
+    if not g.is_cuda or g.dtype != dtype or g.stride(-1) != 1 or g.shape[-1] != n_heads * vdim or gain.shape[0] != n_heads * vdim:
+        raise KernelError("mlstm_output: gate or gain does not fit")
+    out = torch.empty((o.shape[0], n_heads * vdim), dtype=dtype, device=o.device)
+    _check(_fn("mlstm", "bn_mlstm_output")(_ptr(o), _ptr(gain), int(_code(gain)), _ptr(g), int(g_stride), int(_DT[dtype]),
+                                           int(o.shape[0]), int(n_heads), int(vdim), c_float(eps), _ptr(out), _stream()),
+           "mlstm_output")
+    return out
+
+
+# ---- mixture of experts -----------------------------------------------------------------------
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, renormalise: bool = False):
+    """Per token the ``top`` experts with the largest router logits (float32 products), and the logistic
+    function of those logits as weights (divided by their sum with ``renormalise``):
+    ``(ids int32 [T, top], weights float32 [T, top])``."""
+    _need(h, "h", dims=2)
+    _need(w_router, "w_router", dims=2)
+    if w_router.shape[1] != h.shape[1] or not 0 < top <= min(w_router.shape[0], 32) or w_router.shape[0] > 1024:
+        raise KernelError(f"moe_route: router {tuple(w_router.shape)}, top {top} do not fit rows of width {h.shape[1]}")
+    ids = torch.empty((h.shape[0], top), dtype=torch.int32, device=h.device)
+    weights = torch.empty((h.shape[0], top), dtype=torch.float32, device=h.device)
+    _check(_fn("moe", "bn_moe_route")(_ptr(h), int(_code(h)), int(h.shape[0]), int(h.shape[1]), _ptr(w_router),
+                                      int(_code(w_router)), int(w_router.shape[0]), int(top), int(bool(renormalise)),
+                                      _ptr(ids), _ptr(weights), _stream()), "moe_route")
+    return ids, weights
+
+
+def moe_experts_few(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
+                    w_down: torch.Tensor, limit: float, slope: float, scale_input: bool,
+                    add: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The chosen experts of every token, streamed once per (token, expert): float32 ``[T, width]``, the sum over
+    a token's experts plus ``add``.  The weight multiplies the expert's input (``scale_input``) or its output.
+    ``w_gate_up`` ``[experts, 2 * ff, width]`` holds an expert's gate rows and then its up rows, ``w_down``
+    ``[experts, width, ff]``; both in h's type."""
+    _need(h, "h", dims=2)
+    T, width = h.shape
+    _need(ids, "ids", torch.int32, 2)
+    _need(weights, "weights", torch.float32, 2)
+    top = ids.shape[1]
+    _need(w_gate_up, "w_gate_up", h.dtype, 3)
+    _need(w_down, "w_down", h.dtype, 3)
+    E, ff = w_gate_up.shape[0], w_gate_up.shape[1] // 2
+    if (tuple(w_gate_up.shape) != (E, 2 * ff, width) or tuple(w_down.shape) != (E, width, ff)
+            or tuple(ids.shape) != (T, top) or tuple(weights.shape) != (T, top) or width * 4 > 48 * 1024):
+        raise KernelError("moe_experts_few: sizes do not fit")
+    if add is not None:
+        _need(add, "add", dims=2)
+        if tuple(add.shape) != (T, width):
+            raise KernelError("moe_experts_few: add does not fit")
+    y = torch.empty((T * top, ff), dtype=h.dtype, device=h.device)
+    w_up = w_gate_up[:, ff:]
+    _check(_fn("moe", "bn_moe_gate_up")(_ptr(h), int(_code(h)), int(T), int(width), _ptr(ids), _ptr(weights),
+                                        int(bool(scale_input)), _ptr(w_gate_up), c_void_p(w_up.data_ptr()),
+                                        ctypes.c_longlong(2 * ff * width), int(ff), int(top), c_float(limit),
+                                        c_float(slope), _ptr(y), _stream()), "moe_gate_up")
+    out = torch.empty((T, width), dtype=torch.float32, device=h.device)
+    _check(_fn("moe", "bn_moe_down")(_ptr(y), int(_code(y)), int(T), int(ff), _ptr(ids), _ptr(weights),
+                                     int(not scale_input), _ptr(w_down), int(width), int(top), _ptr(add),
+                                     int(_code(add) if add is not None else 0), _ptr(out), _stream()), "moe_down")
+    return out
+
+
+def moe_sort(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, n_experts: int, scale_input: bool):
+    """Sort the (token, expert) items by expert: ``(x_sorted [T * top, width], place int32 [T * top],
+    offsets int32 [experts + 1])``; rows ``offsets[e] .. offsets[e + 1]`` of ``x_sorted`` are the inputs of expert
+    e (times their weight with ``scale_input``), and item i went to row ``place[i]``."""
+    _need(h, "h", dims=2)
+    _need(ids, "ids", torch.int32, 2)
+    _need(weights, "weights", torch.float32, 2)
+    T, width = h.shape
+    top = ids.shape[1]
+    book = torch.zeros(3 * n_experts + 1, dtype=torch.int32, device=h.device)
+    counts, offsets, cursor = book[:n_experts], book[n_experts:2 * n_experts + 1], book[2 * n_experts + 1:]
+    place = torch.empty(T * top, dtype=torch.int32, device=h.device)
+    x_sorted = torch.empty((T * top, width), dtype=h.dtype, device=h.device)
+    _check(_fn("moe", "bn_moe_sort")(_ptr(h), int(_code(h)), int(T), int(width), _ptr(ids), _ptr(weights),
+                                     int(bool(scale_input)), int(top), int(n_experts), _ptr(counts), _ptr(offsets),
+                                     _ptr(cursor), _ptr(place), _ptr(x_sorted), _stream()), "moe_sort")
+    global LAUNCHES
+    LAUNCHES += 2
+    return x_sorted, place, offsets
+
+
+def moe_gather(y_sorted: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, scale_output: bool,
+               add: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 ``[T, width]``: per token the sum of its experts' rows of ``y_sorted`` (times their weight with
+    ``scale_output``), plus ``add``."""
+    _need(y_sorted, "y_sorted", dims=2)
+    _need(place, "place", torch.int32, 1)
+    _need(weights, "weights", torch.float32, 2)
+    T, top = weights.shape
+    width = y_sorted.shape[1]
+    if y_sorted.shape[0] != T * top or place.shape[0] != T * top:
+        raise KernelError("moe_gather: sizes do not fit")
+    if add is not None:
+        _need(add, "add", dims=2)
+        if tuple(add.shape) != (T, width):
+            raise KernelError("moe_gather: add does not fit")
+    out = torch.empty((T, width), dtype=torch.float32, device=y_sorted.device)
+    _check(_fn("moe", "bn_moe_gather")(_ptr(y_sorted), int(_code(y_sorted)), int(T), int(width), _ptr(place), _ptr(weights),
+                                       int(bool(scale_output)), int(top), _ptr(add), int(_code(add) if add is not None else 0),
+                                       _ptr(out), _stream()), "moe_gather")
     return out
 
 

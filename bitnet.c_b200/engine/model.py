@@ -18,7 +18,7 @@ from ..config import ConfigError, ModelSpec, architecture_of, read_config_json
 from ..csrc import build as kernel_build
 from ..csrc import ops
 from ..parts import BuildContext, ParamSpec, Part, build_part
-from ..parts.base import Normed
+from ..parts.base import Cast, Normed
 from .batch import SeqStep, StepContext, pack_step
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -125,6 +125,9 @@ class Model:
         from ..weights import load_weights
         cfg_dict = read_config_json(model_dir)
         arch = architecture_of(cfg_dict)
+        if getattr(arch, "complete_config", None) is not None:
+            from ..weights import tensor_shapes
+            cfg_dict = arch.complete_config(cfg_dict, tensor_shapes(model_dir))
         cfg = arch.read_config(cfg_dict)
         if max_seq:
             cfg = arch.cap_positions(cfg, max_seq)
@@ -233,6 +236,8 @@ class Model:
         sched = self.spec.schedule
         for i, e in enumerate(sched):
             blk = self.blocks[e.block]
+            if isinstance(pending, Cast) and not getattr(blk, "accepts_cast", False):
+                pending = None  # nothing is left to add; this block reads the float32 rows itself
             if diag is not None:
                 if i > 0:
                     ctx.tap("lout", lambda: _residual_after(x, pending))
@@ -253,6 +258,8 @@ class Model:
             ctx.layer = -1
         if ctx.rows is None:
             return None
+        if isinstance(pending, Cast):
+            pending = None
         if isinstance(pending, Normed):
             h = pending.value
         else:
@@ -267,7 +274,7 @@ class Model:
 def _residual_after(x: torch.Tensor, pending) -> torch.Tensor:
     """The residual stream with a block's last delta added (the delta is otherwise added by the next
     norm; a product that prepared that norm in its epilogue has added it already)."""
-    if pending is None or isinstance(pending, Normed):
+    if pending is None or isinstance(pending, (Normed, Cast)):
         return x
     return x + (pending.sum(0) if pending.dim() == 3 else pending).float()
 

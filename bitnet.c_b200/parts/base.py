@@ -58,7 +58,8 @@ class BuildContext:
 @dataclass(frozen=True)
 class KvRequest:
     """Keys and values per token that a mixer wants cached.  Runs whose requests are equal
-    share one storage group; ``window`` > 0 means only the last ``window`` positions are kept.
+    share one storage group; ``window`` > 0 means only the last ``window`` positions are kept, and
+    with ``keep_first`` also the positions below it.
     ``v_head_dim``: the width of a value head when it differs from a key head's (0: the same).
     The library's attention kernels take equal widths; a mixer with others brings its own."""
 
@@ -66,6 +67,7 @@ class KvRequest:
     head_dim: int
     window: int = 0
     v_head_dim: int = 0
+    keep_first: int = 0
 
     @property
     def v_dim(self) -> int:
@@ -149,6 +151,15 @@ class Normed:
         self.value = value
 
 
+class Cast:
+    """The residual stream as it is, already copied into the compute type (``value``): what a block that
+    leaves nothing to add hands to the next one, so that it need not read the float32 rows again.  Only
+    a block with ``accepts_cast = True`` is given one; for every other reader it means "nothing pending"."""
+
+    def __init__(self, value):
+        self.value = value
+
+
 class Norm(Part):
     def add_norm(self, x, delta, ctx, rows=None):
         raise NotImplementedError
@@ -181,6 +192,7 @@ class Block(Part):
     # A block that sets ``accepts_normed`` takes ``pending`` as ``Normed`` too, and a keyword
     # ``next_norm``: the norm that follows this block, whose output its last product may prepare.
     accepts_normed = False
+    accepts_cast = False  # takes ``pending`` as ``Cast`` too
 
     def entry_norm(self):
         """The norm this block applies first (None: not fusable into the block before it)."""

@@ -1,0 +1,126 @@
+"""Softmax attention in its general form: a value width of its own, unit-norm queries and keys, a
+learned bias by distance, a window that keeps the first tokens, a gate per head, shared keys and values."""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from ..csrc import ops
+from .base import KvRequest, Mixer, ParamSpec
+from .registry import register_mixer
+
+
+def distance_buckets(n_buckets: int, max_distance: int) -> torch.Tensor:
+    """The bucket of every distance 0 .. max_distance (int64): a distance below half the number of
+    buckets is its own bucket; from there on buckets widen logarithmically and the last one begins
+    at ``max_distance`` at the latest.  Single precision, as positions are everywhere."""
+    half = n_buckets // 2
+    if n_buckets < 2 or max_distance <= half:
+        raise ValueError(f"{n_buckets} distance buckets up to a distance of {max_distance} cannot be laid out")
+    n = torch.arange(0, max_distance + 1, dtype=torch.float32)
+    far = torch.log(n.clamp(min=1.0) / half) / math.log(max_distance / half) * (n_buckets - half)
+    far = (half + far.floor().to(torch.int64)).clamp(max=n_buckets - 1)
+    return torch.where(n < half, n.to(torch.int64), far)
+
+
+@register_mixer("bias_attention")
+class BiasAttention(Mixer):
+    """q, k, v (and one gate number per head) = W h in one product; q and k divided by their root mean
+    square per head; k (normed) and v appended to the cache; for every head
+    softmax(q k^T * scale + bias[bucket(distance)]) over the keys the window lets through; the head's
+    output times the logistic function of its gate; output projection.  A run without projections of
+    keys and values reads the cache of the run its schedule entry names."""
+
+    kernels = ("linear", "linear_mma", "linear_tc", "gemm_tc", "attention", "unit_norm")
+    graph_safe = True
+
+    def __init__(self, spec, build):
+        super().__init__(spec, build)
+        if spec.n_heads % spec.n_kv_heads:
+            raise ValueError(f"{spec.n_heads} heads are not a multiple of {spec.n_kv_heads} key/value heads")
+        if spec.head_dim % 16 or spec.head_dim > 256 or not 0 < spec.v_head_dim <= 256:
+            raise ValueError(f"head_dim={spec.head_dim} must be a multiple of 16 up to 256, v_head_dim={spec.v_head_dim} at most 256")
+        if not spec.unit_norm:
+            raise ValueError("this mixer is built with unit-norm queries and keys only")
+        self.w_in: Optional[torch.Tensor] = None
+        self.w_o: Optional[torch.Tensor] = None
+        self.rel: Optional[torch.Tensor] = None
+
+    @property
+    def q_dim(self) -> int:
+        return self.spec.n_heads * self.spec.head_dim
+
+    @property
+    def k_dim(self) -> int:
+        return self.spec.n_kv_heads * self.spec.head_dim
+
+    @property
+    def v_dim(self) -> int:
+        return self.spec.n_kv_heads * self.spec.v_head_dim
+
+    def params(self) -> Dict[str, ParamSpec]:
+        s = self.spec
+        p = {"q": ParamSpec((self.q_dim, s.width)), "o": ParamSpec((s.width, s.n_heads * s.v_head_dim))}
+        if s.own_kv:
+            p["k"] = ParamSpec((self.k_dim, s.width))
+            p["v"] = ParamSpec((self.v_dim, s.width))
+        if s.bias_buckets:
+            p["rel"] = ParamSpec((s.bias_buckets, s.n_heads))
+        if s.head_gate:
+            p["g"] = ParamSpec((s.n_heads, s.width))
+        return p
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        s = self.spec
+        parts = [tensors["q"]]
+        self.k_off = self.v_off = self.g_off = 0
+        at = self.q_dim
+        if s.own_kv:
+            parts += [tensors["k"], tensors["v"]]
+            self.k_off, self.v_off = at, at + self.k_dim
+            at += self.k_dim + self.v_dim
+        if s.head_gate:
+            parts.append(tensors["g"])
+            self.g_off = at
+            at += s.n_heads
+        dt = parts[0].dtype if all(t.dtype == parts[0].dtype for t in parts) else torch.float32
+        pad = -at % 8  # rows of the product's result stay 16-byte aligned
+        if pad:
+            parts.append(torch.zeros((pad, s.width), dtype=dt, device=parts[0].device))
+        # one stacked matrix: all projections of the mixer's input are one product
+        self.w_in = torch.cat([t.to(dt) for t in parts], dim=0).contiguous()
+        self.row = at + pad
+        self.w_o = tensors["o"]
+        if s.bias_buckets:
+            # the table by distance instead of by bucket: row n serves distance n, the last row every longer one
+            buckets = distance_buckets(s.bias_buckets, s.bias_max_distance).to(tensors["rel"].device)
+            self.rel = tensors["rel"].float()[buckets].contiguous()
+
+    def cache_request(self) -> KvRequest:
+        s = self.spec
+        return KvRequest(n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window, v_head_dim=s.v_head_dim,
+                         keep_first=s.keep_first if s.window > 0 else 0)
+
+    def forward(self, h, ctx, kv, state):
+        s = self.spec
+        n = h.shape[0]
+        if kv.owner != s.own_kv:
+            raise ValueError("a mixer with key/value projections owns its cache plane, one without reads another's")
+        proj = ops.linear(h, self.w_in, out_dtype=self.build.dtype)
+        if kv.owner:
+            ops.unit_norm_append(proj, s.n_heads, s.head_dim, s.norm_eps, ctx.tok_pos, k_off=self.k_off, v_off=self.v_off,
+                                 n_kv_heads=s.n_kv_heads, tok_seq=ctx.tok_seq, slots=ctx.slots, page_table=kv.page_table,
+                                 k_cache=kv.k, v_cache=kv.v)
+        else:
+            ops.unit_norm_append(proj, s.n_heads, s.head_dim, s.norm_eps, ctx.tok_pos)
+        if ctx.diag is not None:
+            ctx.tap("attn_q", lambda: proj[:, : self.q_dim])
+        out = torch.empty((n, s.n_heads * s.v_head_dim), dtype=self.build.dtype, device=h.device)
+        gate = proj[:, self.g_off:] if s.head_gate else None
+        ops.attention_general(proj, self.row, out, n, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, ctx.tok_seq,
+                              ctx.tok_pos, ctx.slots, kv.page_table, kv.k, kv.v, keep_first=s.keep_first if s.window > 0 else 0,
+                              rel=self.rel, gate=gate, gate_stride=self.row)
+        ctx.tap("attn_out", out)
+        return ops.linear(out, self.w_o, out_dtype=torch.float32)

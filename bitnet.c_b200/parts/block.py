@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 from ..csrc import ops
-from .base import Block, Normed
+from .base import Block, Cast, Normed
 from .registry import build_part, register_block
 
 
@@ -62,3 +62,54 @@ class PreNormBlock(Block):
         d = self.ffn.forward(self._input_for(self.ffn, h), ctx)
         ctx.tap("ffn_out", d)
         return d
+
+
+@register_block("post_norm")
+class PostNormBlock(Block):
+    """x <- norm(alpha x + mixer(x)); x <- norm(alpha x + ffn(x)): the norms follow the sums, and their
+    output is the residual stream itself (float32), which the sublayers read as it is.  Each norm
+    also leaves a copy of its output in the compute type for the products that come next; the last
+    copy goes to the next block as ``Cast``.  Without a feed-forward the second step is skipped, unless
+    the block has a second norm, which then norms alpha x."""
+
+    graph_safe = True  # as far as its parts are
+    accepts_cast = True
+
+    def __init__(self, spec, build):
+        super().__init__(spec, build)
+        self.mixer_norm = build_part("norm", spec.mixer_norm, build)
+        self.mixer = build_part("mixer", spec.mixer, build)
+        self.ffn = build_part("ffn", spec.ffn, build) if spec.ffn is not None else None
+        self.ffn_norm = build_part("norm", spec.ffn_norm, build) if spec.ffn_norm is not None else None
+
+    def children(self):
+        c = {"mixer_norm": self.mixer_norm, "mixer": self.mixer}
+        if self.ffn_norm is not None:
+            c["ffn_norm"] = self.ffn_norm
+        if self.ffn is not None:
+            c["ffn"] = self.ffn
+        return c
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def state_request(self):
+        return self.mixer.state_request()
+
+    def _as_input(self, x):
+        return x if self.build.dtype == x.dtype else x.to(self.build.dtype)
+
+    def forward(self, x, pending, ctx, kv, state):
+        alpha = self.spec.alpha
+        h = pending.value if isinstance(pending, Cast) else self._as_input(x)
+        d = self.mixer.forward(h, ctx, kv, state)
+        ctx.tap("attn_proj", d)
+        h = self.mixer_norm.scaled_add_norm(x, alpha, d)
+        ctx.tap("attn_norm", h)
+        if self.ffn is not None:
+            d = self.ffn.forward(h, ctx)
+            ctx.tap("ffn_out", d)
+            h = self.ffn_norm.scaled_add_norm(x, alpha, d)
+        elif self.ffn_norm is not None and self.ffn_norm.weight is not None:
+            h = self.ffn_norm.scaled_add_norm(x, alpha, None)
+        return Cast(h)

@@ -1,0 +1,77 @@
+"""Mixture of experts with logistic router scores and clamped gated experts."""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..csrc import ops
+from .base import FeedForward, ParamSpec
+from .registry import register_ffn
+
+
+@register_ffn("moe")
+class Moe(FeedForward):
+    """Router logits in float32; each token takes its ``top`` experts with the largest scores
+    s = sigmoid(z) and weights them by s; the weight multiplies the expert's input
+    (``weight_on_input``) or its output.  An expert is down(g * sigmoid(slope g) * (u + 1)) with
+    g = min(gate x, limit), u = clamp(up x, -limit, limit); a shared expert of the same form (sizes and
+    limit of its own) runs for every token and is added.
+
+    Few rows (a decode step): two kernels stream the chosen experts once per (token, expert), from
+    device memory alone.  Many rows: the (token, expert) items are sorted by expert and every expert's
+    rows go through the ordinary products; the host then needs the experts' row counts, one copy per call."""
+
+    kernels = ("linear", "linear_mma", "linear_tc", "gemm_tc", "act", "moe")
+    graph_safe = True  # the steps that are recorded are decode steps, which take the path without the host
+    FEW_ITEMS = 64  # up to so many (token, expert) items the streaming kernels run
+
+    def params(self) -> Dict[str, ParamSpec]:
+        s = self.spec
+        p = {"router": ParamSpec((s.n_experts, s.width))}
+        for e in range(s.n_experts):
+            p[f"e{e}.gate"] = ParamSpec((s.expert_ff, s.width))
+            p[f"e{e}.up"] = ParamSpec((s.expert_ff, s.width))
+            p[f"e{e}.down"] = ParamSpec((s.width, s.expert_ff))
+        if s.shared_ff:
+            p["shared.gate"] = ParamSpec((s.shared_ff, s.width))
+            p["shared.up"] = ParamSpec((s.shared_ff, s.width))
+            p["shared.down"] = ParamSpec((s.width, s.shared_ff))
+        return p
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        s = self.spec
+        dt = self.build.dtype
+        self.w_router = tensors["router"]
+        # [experts, 2 ff, width]: an expert's gate rows, then its up rows; [experts, width, ff]
+        self.w_gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"].to(dt), tensors[f"e{e}.up"].to(dt)], dim=0)
+                                      for e in range(s.n_experts)]).contiguous()
+        self.w_down = torch.stack([tensors[f"e{e}.down"].to(dt) for e in range(s.n_experts)]).contiguous()
+        if s.shared_ff:
+            self.w_shared_gate_up = torch.cat([tensors["shared.gate"].to(dt), tensors["shared.up"].to(dt)], dim=0).contiguous()
+            self.w_shared_down = tensors["shared.down"]
+
+    def _expert(self, x, w_gate_up, w_down, limit, out_dtype):
+        gu = ops.linear(x, w_gate_up, out_dtype=self.build.dtype)
+        act = torch.empty((x.shape[0], gu.shape[1] // 2), dtype=gu.dtype, device=gu.device)
+        ops.glu_limited(gu, act, limit, self.spec.slope)
+        return ops.linear(act, w_down, out_dtype=out_dtype)
+
+    def forward(self, h, ctx):
+        s = self.spec
+        T = h.shape[0]
+        shared = self._expert(h, self.w_shared_gate_up, self.w_shared_down, s.shared_limit, torch.float32) if s.shared_ff else None
+        ids, weights = ops.moe_route(h, self.w_router, s.top, s.renormalise)
+        if ctx.diag is not None:
+            ctx.tap("moe_ids", lambda: ids.float())
+        if ctx.decode or T * s.top <= self.FEW_ITEMS:
+            return ops.moe_experts_few(h, ids, weights, self.w_gate_up, self.w_down, s.expert_limit, s.slope,
+                                       s.weight_on_input, add=shared)
+        x_sorted, place, offsets = ops.moe_sort(h, ids, weights, s.n_experts, s.weight_on_input)
+        at = offsets.cpu().tolist()
+        y_sorted = torch.empty((T * s.top, s.width), dtype=self.build.dtype, device=h.device)
+        for e in range(s.n_experts):
+            if at[e + 1] > at[e]:
+                y_sorted[at[e]: at[e + 1]] = self._expert(x_sorted[at[e]: at[e + 1]], self.w_gate_up[e], self.w_down[e],
+                                                          s.expert_limit, self.build.dtype)
+        return ops.moe_gather(y_sorted, place, weights, not s.weight_on_input, add=shared)

@@ -19,7 +19,7 @@ class RmsNorm(Norm):
     graph_safe = True
 
     def params(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.spec.width,), init="ones")}
+        return {"weight": ParamSpec((self.spec.width,), init="ones", optional=bool(getattr(self.spec, "optional", False)))}
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"]
@@ -36,3 +36,12 @@ class RmsNorm(Norm):
         n = x.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, self.spec.width), dtype=self.build.dtype, device=x.device)
         return ops.add_rmsnorm(x, delta, self.weight, self.spec.eps, out, rows=rows)
+
+    def scaled_add_norm(self, x, alpha, delta):
+        """The norm after the sum: x = norm(alpha * x + delta) in place on the float32 residual; returns
+        the same rows in the compute type (x itself when that is float32)."""
+        if self.build.dtype == torch.float32:
+            ops.scaled_add_rmsnorm(x, alpha, delta, self.weight, self.spec.eps)
+            return x
+        out = torch.empty(x.shape, dtype=self.build.dtype, device=x.device)
+        return ops.scaled_add_rmsnorm(x, alpha, delta, self.weight, self.spec.eps, out)

@@ -62,6 +62,19 @@ def _open_files(model_dir: str) -> List[SafetensorsFile]:
     raise WeightsError(model_dir, [], [], [], ["no model.safetensors and no model.safetensors.index.json"])
 
 
+def tensor_shapes(model_dir: str) -> Dict[str, tuple]:
+    """Name -> shape of every tensor in the folder's safetensors files (headers only; empty if there are none)."""
+    try:
+        files = _open_files(model_dir)
+    except (WeightsError, SafetensorsError):
+        return {}
+    try:
+        return {n: tuple(e.shape) for f in files for n, e in f.entries.items()}
+    finally:
+        for f in files:
+            f.close()
+
+
 def stored_dtype_to_kept(stored: torch.dtype, compute: torch.dtype, integer: bool) -> torch.dtype:
     if integer:
         return torch.int32
