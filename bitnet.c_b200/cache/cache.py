@@ -168,7 +168,10 @@ class Cache:
             if req is not None and cache_of[i] is None:
                 by_request.setdefault(req, []).append(i)
         for req, entries in by_request.items():
-            g = KvGroup(req, entries, n_pages, n_slots, pages_per_seq, dtype, device, allocate)
+            # a windowed plane holds only part of a sequence, so a sequence may be longer than the pool:
+            # its page table reaches as far as the context does (at least 1,024 pages)
+            per_seq = min(pages_for(max_positions), max(n_pages, 1024)) if req.window > 0 else pages_per_seq
+            g = KvGroup(req, entries, n_pages, n_slots, per_seq, dtype, device, allocate)
             for plane, e in enumerate(entries):
                 self._plane[e] = (len(self.groups), plane)
             self.groups.append(g)

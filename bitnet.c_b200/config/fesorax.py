@@ -110,8 +110,8 @@ class FesoraxConfig:
         if heads % kv_heads:
             raise ConfigError(f"config.json: {where}: {heads} heads are not a multiple of {kv_heads} kv_heads")
         dim = _int(m, "dim", where)
-        if dim % 16 or dim > 256:
-            raise ConfigError(f"config.json: {where}.dim={dim} must be a multiple of 16 and at most 256")
+        if dim > 256 or _int(m, "vdim", where) > 256:
+            raise ConfigError(f"config.json: {where}: dim={dim} and vdim={m['vdim']} must be at most 256")
         mask = m.get("mask") or {}
         src = m.get("kv_from")
         if src is not None:

@@ -86,11 +86,15 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
       int p = u < n_first ? u : lo + (u - n_first);
       const T* krow = k_cache + cache_row_offset(pt, p, n_kv_heads, kvh, head_dim);
       float dot = 0.f;
-      for (int d = 0; d < head_dim; d += VN) {
-        float kv[VN];
-        Vec16<T>::load(krow + d, kv);
+      if (head_dim % VN == 0) {  // rows of whole 16-byte pieces
+        for (int d = 0; d < head_dim; d += VN) {
+          float kv[VN];
+          Vec16<T>::load(krow + d, kv);
 #pragma unroll
-        for (int e = 0; e < VN; ++e) dot = fmaf(qs[d + e], kv[e], dot);
+          for (int e = 0; e < VN; ++e) dot = fmaf(qs[d + e], kv[e], dot);
+        }
+      } else {
+        for (int d = 0; d < head_dim; ++d) dot = fmaf(qs[d], to_f32<T>(krow[d]), dot);
       }
       s = dot * scale;
       if (rel) s += rel[(size_t)min(pos - p, n_rel - 1) * n_heads + h];
@@ -138,7 +142,7 @@ extern "C" int bn_attention_general_ex(const void* q, int q_stride, void* out, i
                                        const int* page_table, int pt_stride,
                                        const void* k_cache, const void* v_cache, cudaStream_t stream) {
   if (n_tokens <= 0) return BN_OK;
-  if (head_dim <= 0 || head_dim % 16 || head_dim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads ||
+  if (head_dim <= 0 || head_dim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads ||
       window < 0 || keep_first < 0 || v_dim <= 0 || v_dim > 256 || (rel && n_rel <= 0))
     return BN_ERR_BAD_ARG;
   if (n_heads > 65535) return BN_ERR_BAD_ARG;

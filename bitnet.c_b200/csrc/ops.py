@@ -310,8 +310,8 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
     if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or tuple(k_cache.shape[:3]) != tuple(v_cache.shape[:3]):
         raise KernelError(f"attention: cache {tuple(k_cache.shape)} / {tuple(v_cache.shape)} is not "
                           f"[pages, {n_kv_heads}, {PAGE}, {head_dim} / value width]")
-    if head_dim % 16 or head_dim > 256 or v_dim > 256:
-        raise KernelError(f"attention: head_dim={head_dim} must be a multiple of 16 up to 256, value width {v_dim} at most 256")
+    if not 0 < head_dim <= 256 or v_dim > 256:
+        raise KernelError(f"attention: head_dim={head_dim} and the value width {v_dim} must be at most 256")
     if n_heads % n_kv_heads:
         raise KernelError(f"attention: {n_heads} heads are not a multiple of {n_kv_heads} key/value heads")
     if out.shape[0] < n_tokens or out.shape[1] != n_heads * v_dim:
@@ -894,7 +894,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: 
         raise KernelError(f"linear: x {tuple(x.shape)} and w {tuple(w.shape)} do not share the inner size")
     M, K = x.shape
     N = w.shape[0]
-    few = w.dtype == torch.bfloat16 and K % 8 == 0 and (not swiglu or N % 16 == 0)
+    few = w.dtype == torch.bfloat16 and K % 8 == 0 and (not swiglu or N % 16 == 0) and (N % 8 == 0 or out_dtype is torch.float32)
     small = few and M <= MMA_MAX_ROWS
     streams = few and M <= TC_MAX_ROWS and not partial_sums and USE_TCGEN05
     fast = streams and x.dtype == torch.bfloat16

@@ -40,8 +40,8 @@ class BiasAttention(Mixer):
         super().__init__(spec, build)
         if spec.n_heads % spec.n_kv_heads:
             raise ValueError(f"{spec.n_heads} heads are not a multiple of {spec.n_kv_heads} key/value heads")
-        if spec.head_dim % 16 or spec.head_dim > 256 or not 0 < spec.v_head_dim <= 256:
-            raise ValueError(f"head_dim={spec.head_dim} must be a multiple of 16 up to 256, v_head_dim={spec.v_head_dim} at most 256")
+        if not 0 < spec.head_dim <= 256 or not 0 < spec.v_head_dim <= 256:
+            raise ValueError(f"head_dim={spec.head_dim} and v_head_dim={spec.v_head_dim} must be at most 256")
         if not spec.unit_norm:
             raise ValueError("this mixer is built with unit-norm queries and keys only")
         self.w_in: Optional[torch.Tensor] = None
