@@ -427,6 +427,108 @@ def run_workload(name, repeats=2):
                        "seq_len": cfg["max_position_embeddings"], "new_tokens": new}}
 
 
+# ---- another design beside its closest relative --------------------------------------------------
+def fesorax_sizes(width, heads, kv_heads, dim, m_heads, m_dim, m_vdim, experts, top, ff, shared_ff, window, keep, vocab):
+    """A Fesorax configuration of four layers (attention, mLSTM, attention on the first layer's keys and
+    values, attention) and the Llama configuration of the same width, heads, layers and vocabulary whose
+    feed-forward is as wide as the experts a token uses (top * ff + shared)."""
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5 * 4, "bias_max": 4 * window,
+           "mask": {"size": window, "keep_first": keep}}
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff, "limit": 7.0},
+           "shared": {"ff": shared_ff, "limit": 7.0}}
+    layers = [{"type": "attention", "mixer": dict(att), "mlp": mlp},
+              {"type": "mlstm", "mixer": {"heads": m_heads, "dim": m_dim, "vdim": m_vdim, "gate_cap": 15.0}, "mlp": mlp},
+              {"type": "attention", "mixer": dict(att, kv_from=0), "mlp": mlp},
+              {"type": "attention", "mixer": dict(att), "mlp": mlp}]
+    fes = {"architecture": "Fesorax", "vocab": vocab, "width": width, "postln_alpha": 2.0, "norm": {"eps": 1e-6},
+           "embedding": {"scale": 1.0}, "layers": layers, "max_positions": 8192}
+    llama = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": width,
+             "intermediate_size": top * ff + shared_ff, "num_hidden_layers": len(layers), "num_attention_heads": heads,
+             "num_key_value_heads": kv_heads, "head_dim": dim, "vocab_size": vocab, "max_position_embeddings": 8192,
+             "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "hidden_act": "silu"}
+    return fes, llama
+
+
+DESIGN_SIZES = {
+    "w1024": dict(width=1024, heads=8, kv_heads=2, dim=128, m_heads=4, m_dim=128, m_vdim=256, experts=8, top=2, ff=512,
+                  shared_ff=1024, window=1024, keep=64, vocab=32000),
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, m_heads=8, m_dim=128, m_vdim=256, experts=16, top=2, ff=1024,
+                  shared_ff=2048, window=1024, keep=64, vocab=32000),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, m_heads=16, m_dim=128, m_vdim=256, experts=16, top=2, ff=2048,
+                  shared_ff=4096, window=1024, keep=64, vocab=32000),
+}
+
+
+def kernel_classes(model, vocab, tokens, batch, prompt_len):
+    """Device time by entry point (ms) of one step of ``tokens`` prompt tokens and of one decode step of
+    ``batch`` sequences behind prompts of ``prompt_len``, each kernel between two events (no graph, so the
+    sums exceed the steps' own times by the gaps between launches)."""
+    import torch
+    from bitnet_c_b200.csrc import ops
+    from bitnet_c_b200.engine.batch import SeqStep
+    g = torch.Generator().manual_seed(5)
+    out = {}
+    for name, lens, new in (("prefill", [tokens], None), ("decode", [prompt_len] * batch, 1)):
+        cache = model.new_cache(max_tokens=sum(lens) + 64 * len(lens) + 64, max_seqs=len(lens))
+        slots = [cache.open() for _ in lens]
+        prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lens]
+        for rep in range(2):  # the first pass warms up (and, for decode, fills the cache)
+            torch.cuda.synchronize()
+            if rep == 1:
+                ops.PROFILE = {}
+            if new is None:
+                if rep == 1:
+                    for s in slots:
+                        cache.close(s)
+                    slots = [cache.open() for _ in lens]
+                model.step(cache, [SeqStep(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+            else:
+                if rep == 0:
+                    model.step(cache, [SeqStep(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+                    model.step(cache, [SeqStep(s, [1], [0]) for s in slots])
+                model.step(cache, [SeqStep(s, [2], [0]) for s in slots])
+            torch.cuda.synchronize()
+        prof, ops.PROFILE = ops.PROFILE, None
+        out[name] = {k: round(sum(a.elapsed_time(b) for a, b in v), 4) for k, v in sorted(prof.items())}
+        out[name + "_launches"] = {k: len(v) for k, v in sorted(prof.items())}
+        for s in slots:
+            cache.close(s)
+        del cache
+        torch.cuda.empty_cache()
+    return out
+
+
+def run_design(args):
+    """``--design fesorax``: prefill and decode throughput of the Fesorax design at layer sizes of real
+    models (random weights, bfloat16), beside the Llama decoder of equal width, heads, layers, vocabulary and
+    feed-forward work per token, with each step's device time by kernel entry point."""
+    import torch
+    from bitnet_c_b200.engine import Model
+    pk = peaks()
+    rec = {"metric": "prefill and decode tokens/s of the Fesorax design beside Llama at equal size", "impl": "ours",
+           "dtype": "bf16", "data": "synthetic", "n_gpus": 1, "peaks": pk, "prefill_tokens": PREFILL_TOKENS,
+           "decode_batch": args.batch, "decode_prompt": PROMPT_LEN, "sizes": {}}
+    names = [n for n in DESIGN_SIZES if not args.sizes or n in args.sizes.split(",")]
+    for name in names:
+        fes, llama = fesorax_sizes(**DESIGN_SIZES[name])
+        row = {}
+        for label, cfg in (("fesorax", fes), ("llama", llama)):
+            model = Model.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", norm_std=0.0)
+            shim = {"vocab_size": DESIGN_SIZES[name]["vocab"], "max_position_embeddings": 4096}
+            pre_ms = run_prefill(model, shim)
+            r = run_decode(model, shim, args.batch, args.steps, max(3, args.warmup))
+            row[label] = {"prefill_ms": round(pre_ms, 3), "prefill_tokens_per_s": round(PREFILL_TOKENS / pre_ms * 1e3, 1),
+                          "decode_ms_per_step": round(r["dev_ms"] / args.steps, 4),
+                          "decode_tokens_per_s": round(args.batch * args.steps / r["dev_ms"] * 1e3, 1),
+                          "decode_launches_per_step": r["launches"] // max(1, args.steps),
+                          "kernels_ms": kernel_classes(model, shim["vocab_size"], PREFILL_TOKENS, args.batch, PROMPT_LEN)}
+            del model
+            torch.cuda.empty_cache()
+        rec["sizes"][name] = row
+    print(json.dumps(rec))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -444,6 +546,10 @@ def main():
                          "(comparisons, profiling)")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                     help="compute type of the main decode run (float32: profiling of the 32-bit path, with --skip-points)")
+    ap.add_argument("--design", choices=["fesorax"],
+                    help="measure another design of the library beside Llama at equal size instead (prefill, decode, "
+                         "time by kernel); the default workload and its record stay as they are")
+    ap.add_argument("--sizes", default="", help="with --design: which size sets, with commas (default: all)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -453,6 +559,8 @@ def main():
     if args.workload:
         print(json.dumps(run_workload(args.workload)))
         return 0
+    if args.design:
+        return run_design(args)
     warmup = max(3, args.warmup)
 
     import torch

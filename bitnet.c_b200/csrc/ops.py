@@ -894,7 +894,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: 
         raise KernelError(f"linear: x {tuple(x.shape)} and w {tuple(w.shape)} do not share the inner size")
     M, K = x.shape
     N = w.shape[0]
-    few = w.dtype == torch.bfloat16 and K % 8 == 0 and (not swiglu or N % 16 == 0) and (N % 8 == 0 or out_dtype is torch.float32)
+    few = w.dtype == torch.bfloat16 and K % 8 == 0 and (not swiglu or N % 16 == 0)
     small = few and M <= MMA_MAX_ROWS
     streams = few and M <= TC_MAX_ROWS and not partial_sums and USE_TCGEN05
     fast = streams and x.dtype == torch.bfloat16
