@@ -27,10 +27,17 @@ __device__ __forceinline__ unsigned tile_off(int row, int chunk) {
   return (unsigned)(row * HD * 2 + ((chunk ^ (row & 7)) << 4));
 }
 
-template <int HD>
+// PRECISE: the softmax weights enter the second product as the sum of two bfloat16 numbers (the
+// weight rounded, and what the rounding left), so that they act with 16 bits of mantissa instead of 8:
+// for designs that want their attention weights in single precision.
+__device__ __forceinline__ float bf16_rest(float p) { return p - __bfloat162float(__float2bfloat16_rn(p)); }
+
+template <int HD, bool PRECISE>
 __global__ void __launch_bounds__(PF_THREADS)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
                          int out_stride, int n_heads, int n_kv_heads, int head_dim, float scale_log2e, int window,
+                         int keep_first, const float* __restrict__ rel, int n_rel,
+                         const __nv_bfloat16* __restrict__ gate, int gate_stride,
                          const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
                          const int* __restrict__ seq_start, const int* __restrict__ seq_pos0,
                          const int* __restrict__ slots, const int* __restrict__ page_table, int pt_stride,
@@ -45,6 +52,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
   const unsigned s_q = (unsigned)__cvta_generic_to_shared(smem);
   const unsigned s_k = s_q + PF_M * HD * 2;      // two stages
   const unsigned s_v = s_k + 2 * TILE_BYTES;     // two stages
+  // the head's bias for the distances one tile's scores can have (a span of 127), times log2(e); two stages
+  __shared__ float s_bias[2][PF_THREADS];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   // blocks start in the order of their index, heads fastest: tiles are listed by rising work (the
@@ -63,6 +72,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
   const int q_first = pos0 + row0, q_last = pos0 + row0 + rows_here - 1;
   const int lo_first = window > 0 ? max(0, q_first - window + 1) : 0;
   const int tile_lo = lo_first / PF_N, tile_hi = q_last / PF_N;
+  // with a window, keys at positions below keep_first stay visible: their tiles are walked first
+  const int first_tiles = (window > 0 && keep_first > 0) ? min((keep_first + PF_N - 1) / PF_N, tile_lo) : 0;
+  const int n_walk = first_tiles + tile_hi - tile_lo + 1;
+  auto tile_of = [&](int u) { return u < first_tiles ? u : tile_lo + (u - first_tiles); };
 
   // ---- stage Q (rows beyond the sequence's tokens and dimensions beyond head_dim are zero)
   for (int p = tid; p < PF_M * CHUNKS; p += PF_THREADS) {
@@ -86,7 +99,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
       cp_async16(s_v + stage * TILE_BYTES + tile_off<HD>(r, c), okv ? vb + off : vb, okv);
     }
   };
-  load_kv(tile_lo, 0);
+  load_kv(tile_of(0), 0);
   cp_async_commit();
 
   float o[NT_O][4];
@@ -104,15 +117,19 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     qlo[e] = window > 0 ? max(0, qpos[e] - window + 1) : 0;
   }
 
-  for (int tile = tile_lo; tile <= tile_hi; ++tile) {
-    const int stage = (tile - tile_lo) & 1;
-    if (tile + 1 <= tile_hi) {
-      load_kv(tile + 1, stage ^ 1);
+  for (int u = 0; u < n_walk; ++u) {
+    const int tile = tile_of(u);
+    const int stage = u & 1;
+    if (u + 1 < n_walk) {
+      load_kv(tile_of(u + 1), stage ^ 1);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
+    // distances of this tile's scores: from q_first - (last key of the tile) on
+    const int dist0 = q_first - (tile * PF_N + PF_N - 1);
+    if (rel) s_bias[stage][tid] = rel[(size_t)min(max(dist0 + tid, 0), n_rel - 1) * n_heads + h] * 1.4426950408889634f;
     __syncthreads();
 
     // ---- S = Q K^T for this warp's 16 rows and the tile's 64 keys
@@ -146,8 +163,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
       for (int c = 0; c < 4; ++c) {
         int e = c >> 1;
         int kpos = kbase + j * 8 + 2 * t + (c & 1);
-        bool ok = kpos <= qpos[e] && kpos >= qlo[e];
+        bool ok = kpos <= qpos[e] && (kpos >= qlo[e] || kpos < keep_first);
         float v = ok ? s[j][c] * scale_log2e : -INFINITY;
+        if (rel && ok) v += s_bias[stage][qpos[e] - kpos - dist0];
         s[j][c] = v;
         m_new[e] = fmaxf(m_new[e], v);
       }
@@ -191,6 +209,13 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
       unsigned a1 = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
       unsigned a2 = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
       unsigned a3 = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+      unsigned r0 = 0, r1 = 0, r2 = 0, r3 = 0;
+      if (PRECISE) {
+        r0 = pack_bf16(bf16_rest(s[2 * ks][0]), bf16_rest(s[2 * ks][1]));
+        r1 = pack_bf16(bf16_rest(s[2 * ks][2]), bf16_rest(s[2 * ks][3]));
+        r2 = pack_bf16(bf16_rest(s[2 * ks + 1][0]), bf16_rest(s[2 * ks + 1][1]));
+        r3 = pack_bf16(bf16_rest(s[2 * ks + 1][2]), bf16_rest(s[2 * ks + 1][3]));
+      }
 #pragma unroll
       for (int j = 0; j < NT_O; j += 2) {
         unsigned b0, b1, b2, b3;
@@ -198,6 +223,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
         ldsm_x4_trans(vb + tile_off<HD>(ks * 16 + (mi & 1) * 8 + r, j + (mi >> 1)), b0, b1, b2, b3);
         mma_bf16(o[j], a0, a1, a2, a3, b0, b1);
         mma_bf16(o[j + 1], a0, a1, a2, a3, b2, b3);
+        if (PRECISE) {
+          mma_bf16(o[j], r0, r1, r2, r3, b0, b1);
+          mma_bf16(o[j + 1], r0, r1, r2, r3, b2, b3);
+        }
       }
     }
     __syncthreads();  // the stage is overwritten by the load after next
@@ -214,6 +243,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     int r = warp * 16 + g + e * 8;
     if (r >= rows_here) continue;
     float inv = 1.0f / l_run[e];
+    if (gate) inv *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)(start + row0 + r) * gate_stride + h])));
     __nv_bfloat16* orow = out + (size_t)(start + row0 + r) * out_stride + (size_t)h * head_dim;
 #pragma unroll
     for (int j = 0; j < NT_O; ++j) {
@@ -226,25 +256,26 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
   }
 }
 
-template <int HD>
+template <int HD, bool PRECISE = false>
 static int launch_prefill(const void* q, int q_stride, void* out, int out_stride, int n_tiles, int n_heads,
-                          int n_kv_heads, int head_dim, float scale, int window, const int* tile_seq,
+                          int n_kv_heads, int head_dim, float scale, int window, int keep_first, const float* rel, int n_rel,
+                          const void* gate, int gate_stride, const int* tile_seq,
                           const int* tile_row0, const int* seq_start, const int* seq_pos0, const int* slots,
                           const int* page_table, int pt_stride, const void* k_cache, const void* v_cache,
                           cudaStream_t stream) {
   size_t smem = (size_t)PF_M * HD * 2 + 4 * (size_t)PF_N * HD * 2;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD, PRECISE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
     configured = true;
   }
   if (n_tiles > 65535) return BN_ERR_BAD_ARG;
   dim3 grid(n_heads, n_tiles);
-  BN_LAUNCH((attention_prefill_kernel<HD>), grid, PF_THREADS, smem, stream, 
+  BN_LAUNCH((attention_prefill_kernel<HD, PRECISE>), grid, PF_THREADS, smem, stream, 
       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, head_dim,
-      scale * 1.4426950408889634f, window, tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table, pt_stride,
+      scale * 1.4426950408889634f, window, keep_first, rel, n_rel, (const __nv_bfloat16*)gate, gate_stride, tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table, pt_stride,
       (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache);
   BN_CHECK_LAUNCH();
   return BN_OK;
@@ -253,24 +284,41 @@ static int launch_prefill(const void* q, int q_stride, void* out, int out_stride
 // q: [tokens, q_stride] bfloat16 (head h at element h*head_dim), out [tokens, out_stride].
 // tile_seq / tile_row0: for each block its sequence and the first of its 64 new-token rows;
 // seq_start [n_seqs+1]: first packed row of each sequence; seq_pos0: its length before the step.
+// Optional (0 / null: off): with a window, keys below position keep_first stay visible; rel
+// [n_rel, n_heads] float32 is added to the scaled scores by distance (the last row for every longer
+// one); gate [tokens, gate_stride] holds per token and head a number whose logistic function
+// multiplies the head's output.
+extern "C" int bn_attention_prefill_ex(const void* q, int q_stride, void* out, int out_stride, int n_tiles, int n_heads,
+                                       int n_kv_heads, int head_dim, float scale, int window, int keep_first,
+                                       const float* rel, int n_rel, const void* gate, int gate_stride, int precise,
+                                       const int* tile_seq, const int* tile_row0, const int* seq_start,
+                                       const int* seq_pos0, const int* slots, const int* page_table, int pt_stride,
+                                       const void* k_cache, const void* v_cache, cudaStream_t stream) {
+  if (n_tiles <= 0) return BN_OK;
+  if (head_dim <= 0 || head_dim % 16 || head_dim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads || window < 0 ||
+      n_heads > 65535 || (q_stride % 8) || (out_stride % 2) || (((uintptr_t)q) & 15) || keep_first < 0 ||
+      (rel && n_rel <= 0))
+    return BN_ERR_BAD_ARG;
+#define BN_PF_ARGS q, q_stride, out, out_stride, n_tiles, n_heads, n_kv_heads, head_dim, scale, window, keep_first, rel, \
+                   n_rel, gate, gate_stride, tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table, pt_stride,      \
+                   k_cache, v_cache, stream
+  if (precise) {
+    if (head_dim <= 64) return launch_prefill<64, true>(BN_PF_ARGS);
+    if (head_dim <= 128) return launch_prefill<128, true>(BN_PF_ARGS);
+    return launch_prefill<256, true>(BN_PF_ARGS);
+  }
+  if (head_dim <= 64) return launch_prefill<64>(BN_PF_ARGS);
+  if (head_dim <= 128) return launch_prefill<128>(BN_PF_ARGS);
+  return launch_prefill<256>(BN_PF_ARGS);
+#undef BN_PF_ARGS
+}
+
 extern "C" int bn_attention_prefill(const void* q, int q_stride, void* out, int out_stride, int n_tiles, int n_heads,
                                     int n_kv_heads, int head_dim, float scale, int window, const int* tile_seq,
                                     const int* tile_row0, const int* seq_start, const int* seq_pos0,
                                     const int* slots, const int* page_table, int pt_stride, const void* k_cache,
                                     const void* v_cache, cudaStream_t stream) {
-  if (n_tiles <= 0) return BN_OK;
-  if (head_dim <= 0 || head_dim % 16 || head_dim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads || window < 0 ||
-      n_heads > 65535 || (q_stride % 8) || (out_stride % 2) || (((uintptr_t)q) & 15))
-    return BN_ERR_BAD_ARG;
-  if (head_dim <= 64)
-    return launch_prefill<64>(q, q_stride, out, out_stride, n_tiles, n_heads, n_kv_heads, head_dim, scale, window,
-                              tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table, pt_stride, k_cache, v_cache,
-                              stream);
-  if (head_dim <= 128)
-    return launch_prefill<128>(q, q_stride, out, out_stride, n_tiles, n_heads, n_kv_heads, head_dim, scale, window,
-                               tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table, pt_stride, k_cache,
-                               v_cache, stream);
-  return launch_prefill<256>(q, q_stride, out, out_stride, n_tiles, n_heads, n_kv_heads, head_dim, scale, window,
-                             tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table, pt_stride, k_cache, v_cache,
-                             stream);
+  return bn_attention_prefill_ex(q, q_stride, out, out_stride, n_tiles, n_heads, n_kv_heads, head_dim, scale, window, 0,
+                                 nullptr, 0, nullptr, 0, 0, tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table,
+                                 pt_stride, k_cache, v_cache, stream);
 }

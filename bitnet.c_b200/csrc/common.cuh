@@ -127,6 +127,47 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Dot product of n numbers in shared memory (float32) with a row of weights in global memory, by one
+// warp: rows of whole 16-byte pieces are read in such pieces (8 bfloat16 or 4 float32 per lane and
+// turn), others number by number.  Every lane gets the result.
+__device__ __forceinline__ float warp_dot(const float* __restrict__ xs, const __nv_bfloat16* __restrict__ w, int n, int lane) {
+  float acc = 0.f;
+  if ((n & 7) == 0 && (((uintptr_t)w) & 15) == 0) {
+    for (int c = lane * 8; c < n; c += 256) {
+      uint4 raw = *reinterpret_cast<const uint4*>(w + c);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 f = __bfloat1622float2(h2[i]);
+        acc = fmaf(xs[c + 2 * i], f.x, acc);
+        acc = fmaf(xs[c + 2 * i + 1], f.y, acc);
+      }
+    }
+  } else {
+    for (int c = lane; c < n; c += 32) acc = fmaf(xs[c], __bfloat162float(w[c]), acc);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  return acc;
+}
+__device__ __forceinline__ float warp_dot(const float* __restrict__ xs, const float* __restrict__ w, int n, int lane) {
+  float acc = 0.f;
+  if ((n & 3) == 0 && (((uintptr_t)w) & 15) == 0) {
+    for (int c = lane * 4; c < n; c += 128) {
+      float4 f = *reinterpret_cast<const float4*>(w + c);
+      acc = fmaf(xs[c], f.x, acc);
+      acc = fmaf(xs[c + 1], f.y, acc);
+      acc = fmaf(xs[c + 2], f.z, acc);
+      acc = fmaf(xs[c + 3], f.w, acc);
+    }
+  } else {
+    for (int c = lane; c < n; c += 32) acc = fmaf(xs[c], w[c], acc);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  return acc;
+}
+
 // Block-wide sum for blocks of up to 1024 threads; `scratch` holds 32 floats.
 // Every thread gets the result.  The order of additions depends only on the
 // block size, never on what else runs, so a row's result does not change with

@@ -26,14 +26,14 @@ __global__ void mlstm_gates_kernel(const T* __restrict__ h, int width, const W* 
                                    const W* __restrict__ bias, int n_heads, float cap, float* __restrict__ gates) {
   pdl_launch_dependents();
   pdl_wait();
+  extern __shared__ float xs[];  // width
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
   const T* row = h + (size_t)t * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) xs[c] = to_f32<T>(row[c]);
+  __syncthreads();
   for (int r = warp; r < 2 * n_heads; r += n_warps) {
-    const W* wr = w + (size_t)r * width;
-    float dot = 0.f;
-    for (int c = lane; c < width; c += 32) dot = fmaf(to_f32<T>(row[c]), to_f32<W>(wr[c]), dot);
-    dot = warp_sum(dot);
+    float dot = warp_dot(xs, w + (size_t)r * width, width, lane);
     if (lane == 0) {
       float z = cap * tanhf((dot + to_f32<W>(bias[r])) / cap);
       if (r >= n_heads) z = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));  // log(sigmoid(z))
@@ -45,15 +45,17 @@ __global__ void mlstm_gates_kernel(const T* __restrict__ h, int width, const W* 
 extern "C" int bn_mlstm_gates(const void* h, int h_dtype, int n_tokens, int width, const void* w, const void* bias,
                               int w_dtype, int n_heads, float cap, float* gates, cudaStream_t stream) {
   if (n_tokens <= 0) return BN_OK;
-  if (!h || !w || !bias || !gates || width <= 0 || n_heads <= 0 || !(cap > 0.f)) return BN_ERR_BAD_ARG;
+  if (!h || !w || !bias || !gates || width <= 0 || n_heads <= 0 || !(cap > 0.f) || (size_t)width * sizeof(float) > 48 * 1024)
+    return BN_ERR_BAD_ARG;
+  const size_t smem = (size_t)width * sizeof(float);
   if (h_dtype == BN_F32 && w_dtype == BN_F32)
-    BN_LAUNCH((mlstm_gates_kernel<float, float>), n_tokens, ML_GATE_THREADS, 0, stream, (const float*)h, width,
+    BN_LAUNCH((mlstm_gates_kernel<float, float>), n_tokens, ML_GATE_THREADS, smem, stream, (const float*)h, width,
               (const float*)w, (const float*)bias, n_heads, cap, gates);
   else if (h_dtype == BN_BF16 && w_dtype == BN_BF16)
-    BN_LAUNCH((mlstm_gates_kernel<__nv_bfloat16, __nv_bfloat16>), n_tokens, ML_GATE_THREADS, 0, stream,
+    BN_LAUNCH((mlstm_gates_kernel<__nv_bfloat16, __nv_bfloat16>), n_tokens, ML_GATE_THREADS, smem, stream,
               (const __nv_bfloat16*)h, width, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, n_heads, cap, gates);
   else if (h_dtype == BN_BF16 && w_dtype == BN_F32)
-    BN_LAUNCH((mlstm_gates_kernel<__nv_bfloat16, float>), n_tokens, ML_GATE_THREADS, 0, stream,
+    BN_LAUNCH((mlstm_gates_kernel<__nv_bfloat16, float>), n_tokens, ML_GATE_THREADS, smem, stream,
               (const __nv_bfloat16*)h, width, (const float*)w, (const float*)bias, n_heads, cap, gates);
   else
     return BN_ERR_BAD_ARG;
@@ -125,6 +127,108 @@ __global__ void mlstm_recurrence_kernel(const T* __restrict__ qkv, int row_strid
   }
 }
 
+// Head sizes up to 128: one warp per (sequence, head, 32 value columns), the lane's column of S in
+// registers (D of them, dim padded with zeros), n spread over the lanes, q and k of the token handed
+// round through shared memory.  No barrier but the warp's own; the next token's row is requested
+// while this one's is worked on.  The arithmetic is that of the kernel above, term by term.
+template <typename T, int D>
+__global__ void __launch_bounds__(32) mlstm_recurrence_warp_kernel(
+    const T* __restrict__ qkv, int row_stride, int k_off, int v_off, const float* __restrict__ gates,
+    float* __restrict__ state, const int* __restrict__ seq_start, const int* __restrict__ slots, int n_heads, int dim,
+    int vdim, float q_scale, float* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int R = D / 32;
+  __shared__ __align__(16) float sq[D], sk[D];
+  const int seq = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
+  const int c = blockIdx.z * 32 + lane;
+  const bool has_col = c < vdim;
+  const size_t per_head = (size_t)dim * vdim + dim + 1;
+  float* st = state + ((size_t)slots[seq] * n_heads + head) * per_head;
+  float* st_n = st + (size_t)dim * vdim;
+  float S[D];
+#pragma unroll
+  for (int d = 0; d < D; ++d) S[d] = (has_col && d < dim) ? st[(size_t)d * vdim + c] : 0.f;
+  float n[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) n[r] = (lane + 32 * r < dim) ? st_n[lane + 32 * r] : 0.f;
+  float m = st_n[dim];
+  const int t0 = seq_start[seq], t1 = seq_start[seq + 1];
+  float qn[R], kn[R], vn = 0.f, gi_n = 0.f, gf_n = 0.f;
+  auto fetch = [&](int t) {
+    const T* row = qkv + (size_t)t * row_stride;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      int d = lane + 32 * r;
+      qn[r] = d < dim ? to_f32<T>(row[(size_t)head * dim + d]) * q_scale : 0.f;
+      kn[r] = d < dim ? to_f32<T>(row[k_off + (size_t)head * dim + d]) : 0.f;
+    }
+    vn = has_col ? to_f32<T>(row[v_off + (size_t)head * vdim + c]) : 0.f;
+    gi_n = gates[(size_t)t * 2 * n_heads + head];
+    gf_n = gates[(size_t)t * 2 * n_heads + n_heads + head];
+  };
+  if (t0 < t1) fetch(t0);
+  for (int t = t0; t < t1; ++t) {
+    float q[R], k[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) { q[r] = qn[r]; k[r] = kn[r]; }
+    const float v = vn, gi = gi_n, gf = gf_n;
+    __syncwarp();  // the step before has read sq, sk
+#pragma unroll
+    for (int r = 0; r < R; ++r) { sq[lane + 32 * r] = q[r]; sk[lane + 32 * r] = k[r]; }
+    if (t + 1 < t1) fetch(t + 1);
+    float m_new = fmaxf(gf + m, gi);
+    float a = expf(gf + m - m_new), b = expf(gi - m_new);
+    m = m_new;
+    float nq = 0.f;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      n[r] = a * n[r] + b * k[r];
+      nq = fmaf(n[r], q[r], nq);
+    }
+    // the same order of additions as the kernel above: lane l adds its d = l, l + 32, ..., then the lanes meet
+    nq = warp_sum(nq);
+    float denom = fmaxf(fabsf(nq), expf(-m)) + 1e-6f;
+    __syncwarp();
+    float bv = b * v, acc = 0.f;
+#pragma unroll
+    for (int d4 = 0; d4 < D; d4 += 4) {
+      float4 k4 = *reinterpret_cast<const float4*>(sk + d4), q4 = *reinterpret_cast<const float4*>(sq + d4);
+      S[d4] = fmaf(a, S[d4], bv * k4.x);         acc = fmaf(S[d4], q4.x, acc);
+      S[d4 + 1] = fmaf(a, S[d4 + 1], bv * k4.y); acc = fmaf(S[d4 + 1], q4.y, acc);
+      S[d4 + 2] = fmaf(a, S[d4 + 2], bv * k4.z); acc = fmaf(S[d4 + 2], q4.z, acc);
+      S[d4 + 3] = fmaf(a, S[d4 + 3], bv * k4.w); acc = fmaf(S[d4 + 3], q4.w, acc);
+    }
+    if (has_col) out[(size_t)t * n_heads * vdim + (size_t)head * vdim + c] = acc / denom;
+  }
+  if (has_col) {
+#pragma unroll
+    for (int d = 0; d < D; ++d)
+      if (d < dim) st[(size_t)d * vdim + c] = S[d];
+  }
+  if (blockIdx.z == 0) {
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      if (lane + 32 * r < dim) st_n[lane + 32 * r] = n[r];
+    if (lane == 0) st_n[dim] = m;
+  }
+}
+
+template <typename T>
+static cudaError_t launch_mlstm_warp(const void* qkv, int row_stride, int k_off, int v_off, const float* gates, float* state,
+                                     const int* seq_start, const int* slots, int n_seqs, int n_heads, int dim, int vdim,
+                                     float q_scale, float* out, cudaStream_t stream) {
+  dim3 grid(n_seqs, n_heads, (vdim + 31) / 32);
+  if (dim <= 32)
+    return bn_launch(mlstm_recurrence_warp_kernel<T, 32>, grid, dim3(32), 0, stream, (const T*)qkv, row_stride, k_off, v_off,
+                     gates, state, seq_start, slots, n_heads, dim, vdim, q_scale, out);
+  if (dim <= 64)
+    return bn_launch(mlstm_recurrence_warp_kernel<T, 64>, grid, dim3(32), 0, stream, (const T*)qkv, row_stride, k_off, v_off,
+                     gates, state, seq_start, slots, n_heads, dim, vdim, q_scale, out);
+  return bn_launch(mlstm_recurrence_warp_kernel<T, 128>, grid, dim3(32), 0, stream, (const T*)qkv, row_stride, k_off, v_off,
+                   gates, state, seq_start, slots, n_heads, dim, vdim, q_scale, out);
+}
+
 // qkv: rows of the new tokens with the query heads at element 0, key heads at k_off, value heads at
 // v_off; gates [n_tokens, 2 * heads]; state [slots, heads, dim * vdim + dim + 1]; out [n_tokens, heads * vdim] float32.
 extern "C" int bn_mlstm_recurrence(const void* qkv, int dtype, int row_stride, int k_off, int v_off, const float* gates,
@@ -132,6 +236,16 @@ extern "C" int bn_mlstm_recurrence(const void* qkv, int dtype, int row_stride, i
                                    int vdim, float q_scale, float* out, cudaStream_t stream) {
   if (n_seqs <= 0) return BN_OK;
   if (!qkv || !gates || !state || !out || n_heads <= 0 || dim <= 0 || vdim <= 0 || n_heads > 65535) return BN_ERR_BAD_ARG;
+  if (dim <= 128 && (vdim + 31) / 32 <= 65535 && (dtype == BN_F32 || dtype == BN_BF16)) {
+    cudaError_t e = dtype == BN_F32
+        ? launch_mlstm_warp<float>(qkv, row_stride, k_off, v_off, gates, state, seq_start, slots, n_seqs, n_heads, dim, vdim,
+                                   q_scale, out, stream)
+        : launch_mlstm_warp<__nv_bfloat16>(qkv, row_stride, k_off, v_off, gates, state, seq_start, slots, n_seqs, n_heads, dim,
+                                           vdim, q_scale, out, stream);
+    if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
+    BN_CHECK_LAUNCH();
+    return BN_OK;
+  }
   int cols = vdim >= 128 ? 128 : (vdim + 31) / 32 * 32;
   while (cols > 32 && ((size_t)dim * cols + 3 * dim) * sizeof(float) > 160 * 1024) cols /= 2;
   size_t smem = ((size_t)dim * cols + 3 * (size_t)dim) * sizeof(float);

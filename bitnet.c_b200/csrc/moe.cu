@@ -27,14 +27,14 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int width, const W* __
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float z[MOE_MAX_EXPERTS];
+  extern __shared__ float xs[];  // width
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
   const T* row = h + (size_t)t * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) xs[c] = to_f32<T>(row[c]);
+  __syncthreads();
   for (int e = warp; e < n_experts; e += n_warps) {
-    const W* wr = w + (size_t)e * width;
-    float dot = 0.f;
-    for (int c = lane; c < width; c += 32) dot = fmaf(to_f32<T>(row[c]), to_f32<W>(wr[c]), dot);
-    dot = warp_sum(dot);
+    float dot = warp_dot(xs, w + (size_t)e * width, width, lane);
     if (lane == 0) z[e] = dot;
   }
   __syncthreads();
@@ -68,16 +68,17 @@ extern "C" int bn_moe_route(const void* h, int h_dtype, int n_tokens, int width,
                             int n_experts, int top, int renormalise, int* ids, float* weights, cudaStream_t stream) {
   if (n_tokens <= 0) return BN_OK;
   if (!h || !w || !ids || !weights || width <= 0 || n_experts <= 0 || n_experts > MOE_MAX_EXPERTS || top <= 0 ||
-      top > n_experts || top > 32)
+      top > n_experts || top > 32 || (size_t)width * sizeof(float) > 40 * 1024)
     return BN_ERR_BAD_ARG;
+  const size_t smem = (size_t)width * sizeof(float);
   if (h_dtype == BN_F32 && w_dtype == BN_F32)
-    BN_LAUNCH((moe_route_kernel<float, float>), n_tokens, 128, 0, stream, (const float*)h, width, (const float*)w,
+    BN_LAUNCH((moe_route_kernel<float, float>), n_tokens, 256, smem, stream, (const float*)h, width, (const float*)w,
               n_experts, top, renormalise, ids, weights);
   else if (h_dtype == BN_BF16 && w_dtype == BN_BF16)
-    BN_LAUNCH((moe_route_kernel<__nv_bfloat16, __nv_bfloat16>), n_tokens, 128, 0, stream, (const __nv_bfloat16*)h, width,
+    BN_LAUNCH((moe_route_kernel<__nv_bfloat16, __nv_bfloat16>), n_tokens, 256, smem, stream, (const __nv_bfloat16*)h, width,
               (const __nv_bfloat16*)w, n_experts, top, renormalise, ids, weights);
   else if (h_dtype == BN_BF16 && w_dtype == BN_F32)
-    BN_LAUNCH((moe_route_kernel<__nv_bfloat16, float>), n_tokens, 128, 0, stream, (const __nv_bfloat16*)h, width,
+    BN_LAUNCH((moe_route_kernel<__nv_bfloat16, float>), n_tokens, 256, smem, stream, (const __nv_bfloat16*)h, width,
               (const float*)w, n_experts, top, renormalise, ids, weights);
   else
     return BN_ERR_BAD_ARG;
@@ -109,15 +110,8 @@ __global__ void moe_gate_up_kernel(const T* __restrict__ h, int width, const int
   __syncthreads();
   const int j0 = blockIdx.y * MOE_ROWS_PER_BLOCK, j1 = min(ff, j0 + MOE_ROWS_PER_BLOCK);
   for (int j = j0 + warp; j < j1; j += n_warps) {
-    const T* gr = w_gate + (size_t)e * expert_stride + (size_t)j * width;
-    const T* ur = w_up + (size_t)e * expert_stride + (size_t)j * width;
-    float g = 0.f, u = 0.f;
-    for (int c = lane; c < width; c += 32) {
-      g = fmaf(xs[c], to_f32<T>(gr[c]), g);
-      u = fmaf(xs[c], to_f32<T>(ur[c]), u);
-    }
-    g = warp_sum(g);
-    u = warp_sum(u);
+    float g = warp_dot(xs, w_gate + (size_t)e * expert_stride + (size_t)j * width, width, lane);
+    float u = warp_dot(xs, w_up + (size_t)e * expert_stride + (size_t)j * width, width, lane);
     if (lane == 0) {
       // the products' results pass through the compute type, as they do on the sorted path
       g = fminf(to_f32<T>(from_f32<T>(g)), limit);
@@ -134,18 +128,17 @@ __global__ void moe_down_kernel(const T* __restrict__ y, int ff, const int* __re
                                 int width, int top, const void* __restrict__ add, int add_dtype, float* __restrict__ out) {
   pdl_launch_dependents();
   pdl_wait();
+  extern __shared__ float ys[];  // top * ff: the token's activations, expert by expert
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < top * ff; i += blockDim.x) ys[i] = to_f32<T>(y[(size_t)t * top * ff + i]);
+  __syncthreads();
   const int c0 = blockIdx.y * MOE_ROWS_PER_BLOCK, c1 = min(width, c0 + MOE_ROWS_PER_BLOCK);
   for (int c = c0 + warp; c < c1; c += n_warps) {
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
       const int e = ids[(size_t)t * top + k];
-      const T* wr = w_down + ((size_t)e * width + c) * ff;
-      const T* yr = y + ((size_t)t * top + k) * ff;
-      float dot = 0.f;
-      for (int j = lane; j < ff; j += 32) dot = fmaf(to_f32<T>(yr[j]), to_f32<T>(wr[j]), dot);
-      dot = warp_sum(dot);
+      float dot = warp_dot(ys + (size_t)k * ff, w_down + ((size_t)e * width + c) * ff, ff, lane);
       total += scale_output ? dot * weights[(size_t)t * top + k] : dot;
     }
     if (lane == 0) {
@@ -182,11 +175,13 @@ extern "C" int bn_moe_down(const void* y, int dtype, int n_tokens, int ff, const
   if (n_tokens <= 0) return BN_OK;
   if (!y || !ids || !weights || !w_down || !out || width <= 0 || ff <= 0 || top <= 0) return BN_ERR_BAD_ARG;
   dim3 grid(n_tokens, (width + MOE_ROWS_PER_BLOCK - 1) / MOE_ROWS_PER_BLOCK);
+  const size_t smem = (size_t)top * ff * sizeof(float);
+  if (smem > 48 * 1024) return BN_ERR_BAD_ARG;
   if (dtype == BN_F32)
-    BN_LAUNCH(moe_down_kernel<float>, grid, MOE_THREADS, 0, stream, (const float*)y, ff, ids, weights, scale_output,
+    BN_LAUNCH(moe_down_kernel<float>, grid, MOE_THREADS, smem, stream, (const float*)y, ff, ids, weights, scale_output,
               (const float*)w_down, width, top, add, add_dtype, out);
   else if (dtype == BN_BF16)
-    BN_LAUNCH(moe_down_kernel<__nv_bfloat16>, grid, MOE_THREADS, 0, stream, (const __nv_bfloat16*)y, ff, ids, weights,
+    BN_LAUNCH(moe_down_kernel<__nv_bfloat16>, grid, MOE_THREADS, smem, stream, (const __nv_bfloat16*)y, ff, ids, weights,
               scale_output, (const __nv_bfloat16*)w_down, width, top, add, add_dtype, out);
   else
     return BN_ERR_BAD_ARG;

@@ -343,9 +343,13 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
 def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                       scale: float, window: int, tile_seq: torch.Tensor, tile_row0: torch.Tensor,
                       seq_start: torch.Tensor, seq_pos0: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
-                      k_cache: torch.Tensor, v_cache: torch.Tensor) -> torch.Tensor:
+                      k_cache: torch.Tensor, v_cache: torch.Tensor, *, keep_first: int = 0,
+                      rel: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, gate_stride: int = 0,
+                      precise: bool = False) -> torch.Tensor:
     """bfloat16 causal attention of runs of new tokens on the tensor cores; block i handles up to 64
-    new tokens of sequence tile_seq[i] from its row tile_row0[i] on."""
+    new tokens of sequence tile_seq[i] from its row tile_row0[i] on.  ``keep_first``, ``rel`` and ``gate`` as
+    for ``attention_general``; ``precise``: the softmax weights enter the second product with 16 bits of
+    mantissa (as two bfloat16 terms) instead of 8."""
     if not q.is_cuda or q.stride(-1) != 1 or q.dtype != torch.bfloat16:
         raise KernelError("attention_prefill: q must be a bfloat16 CUDA tensor with unit inner stride")
     _need(out, "out", torch.bfloat16, 2)
@@ -361,6 +365,22 @@ def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_heads
         raise KernelError(f"attention_prefill: head_dim={head_dim}, heads {n_heads}/{n_kv_heads} not supported")
     if out.shape[1] != n_heads * head_dim or q_stride % 8:
         raise KernelError("attention_prefill: out or q_stride does not fit")
+    n_rel = 0
+    if rel is not None:
+        _need(rel, "rel", torch.float32, 2)
+        if rel.shape[1] != n_heads or rel.shape[0] < 1:
+            raise KernelError(f"attention_prefill: bias table {tuple(rel.shape)} is not [distances, {n_heads}]")
+        n_rel = rel.shape[0]
+    if gate is not None and (not gate.is_cuda or gate.dtype != torch.bfloat16 or gate.stride(-1) != 1
+                             or gate.shape[-1] < n_heads or gate_stride <= 0):
+        raise KernelError("attention_prefill: gate must be a bfloat16 CUDA view with unit inner stride and one number per head")
+    if keep_first or rel is not None or gate is not None or precise:
+        _check(_fn("attention_prefill", "bn_attention_prefill_ex")(
+            _ptr(q), int(q_stride), _ptr(out), int(out.shape[1]), int(tile_seq.shape[0]), int(n_heads),
+            int(n_kv_heads), int(head_dim), c_float(scale), int(window), int(keep_first), _ptr(rel), int(n_rel), _ptr(gate),
+            int(gate_stride), int(bool(precise)), _ptr(tile_seq), _ptr(tile_row0), _ptr(seq_start), _ptr(seq_pos0), _ptr(slots),
+            _ptr(page_table), int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), _stream()), "attention_prefill")
+        return out
     _check(_fn("attention_prefill", "bn_attention_prefill")(
         _ptr(q), int(q_stride), _ptr(out), int(out.shape[1]), int(tile_seq.shape[0]), int(n_heads),
         int(n_kv_heads), int(head_dim), c_float(scale), int(window), _ptr(tile_seq), _ptr(tile_row0),
@@ -1126,6 +1146,20 @@ def moe_gather(y_sorted: torch.Tensor, place: torch.Tensor, weights: torch.Tenso
                                        int(bool(scale_output)), int(top), _ptr(add), int(_code(add) if add is not None else 0),
                                        _ptr(out), _stream()), "moe_gather")
     return out
+
+
+def matmul_into(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = x . w^T by the library product, written into ``out`` (a slice of a larger buffer, say): for
+    many products of many rows whose results lie side by side.  float32 products are true float32."""
+    _need(x, "x", dims=2)
+    _need(w, "w", x.dtype, 2)
+    _need(out, "out", x.dtype, 2)
+    if x.shape[1] != w.shape[1] or tuple(out.shape) != (x.shape[0], w.shape[0]):
+        raise KernelError(f"matmul_into: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
+    if w.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
+        raise KernelError("float32 products need torch.backends.cuda.matmul.allow_tf32 = False")
+    product = lambda: torch.matmul(x, w.t(), out=out)
+    return product() if PROFILE is None else _timed("library.matmul", product)
 
 
 # ---- sampling -----------------------------------------------------------------------------

@@ -33,7 +33,8 @@ class BiasAttention(Mixer):
     output times the logistic function of its gate; output projection.  A run without projections of
     keys and values reads the cache of the run its schedule entry names."""
 
-    kernels = ("linear", "linear_mma", "linear_tc", "gemm_tc", "attention", "unit_norm")
+    kernels = ("linear", "linear_mma", "linear_tc", "gemm_tc", "attention", "attention_prefill", "unit_norm")
+    TILED_MIN_TOKENS = 16  # runs of new tokens from this many on take the tensor-core kernel (bfloat16)
     graph_safe = True
 
     def __init__(self, spec, build):
@@ -119,8 +120,17 @@ class BiasAttention(Mixer):
             ctx.tap("attn_q", lambda: proj[:, : self.q_dim])
         out = torch.empty((n, s.n_heads * s.v_head_dim), dtype=self.build.dtype, device=h.device)
         gate = proj[:, self.g_off:] if s.head_gate else None
-        ops.attention_general(proj, self.row, out, n, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, ctx.tok_seq,
-                              ctx.tok_pos, ctx.slots, kv.page_table, kv.k, kv.v, keep_first=s.keep_first if s.window > 0 else 0,
-                              rel=self.rel, gate=gate, gate_stride=self.row)
+        keep = s.keep_first if s.window > 0 else 0
+        if (self.build.dtype == torch.bfloat16 and not ctx.decode and ctx.tile_seq is not None and ctx.max_new >= self.TILED_MIN_TOKENS
+                and s.v_head_dim == s.head_dim and s.head_dim % 16 == 0):
+            # runs of new tokens: 64 tokens of a sequence and a head per block on the tensor cores, the
+            # softmax weights with 16 bits of mantissa
+            ops.attention_prefill(proj, self.row, out, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, ctx.tile_seq,
+                                  ctx.tile_row0, ctx.seq_start, ctx.seq_pos0, ctx.slots, kv.page_table, kv.k, kv.v,
+                                  keep_first=keep, rel=self.rel, gate=gate, gate_stride=self.row, precise=True)
+        else:
+            ops.attention_general(proj, self.row, out, n, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, ctx.tok_seq,
+                                  ctx.tok_pos, ctx.slots, kv.page_table, kv.k, kv.v, keep_first=keep,
+                                  rel=self.rel, gate=gate, gate_stride=self.row)
         ctx.tap("attn_out", out)
         return ops.linear(out, self.w_o, out_dtype=torch.float32)

@@ -69,9 +69,16 @@ class Moe(FeedForward):
                                        s.weight_on_input, add=shared)
         x_sorted, place, offsets = ops.moe_sort(h, ids, weights, s.n_experts, s.weight_on_input)
         at = offsets.cpu().tolist()
-        y_sorted = torch.empty((T * s.top, s.width), dtype=self.build.dtype, device=h.device)
+        dt, dev_ = self.build.dtype, h.device
+        # every expert's rows lie side by side: its two products write into slices, the activation runs once
+        gate_up = torch.empty((T * s.top, 2 * s.expert_ff), dtype=dt, device=dev_)
         for e in range(s.n_experts):
             if at[e + 1] > at[e]:
-                y_sorted[at[e]: at[e + 1]] = self._expert(x_sorted[at[e]: at[e + 1]], self.w_gate_up[e], self.w_down[e],
-                                                          s.expert_limit, self.build.dtype)
+                ops.matmul_into(x_sorted[at[e]: at[e + 1]], self.w_gate_up[e], gate_up[at[e]: at[e + 1]])
+        act = torch.empty((T * s.top, s.expert_ff), dtype=dt, device=dev_)
+        ops.glu_limited(gate_up, act, s.expert_limit, s.slope)
+        y_sorted = torch.empty((T * s.top, s.width), dtype=dt, device=dev_)
+        for e in range(s.n_experts):
+            if at[e + 1] > at[e]:
+                ops.matmul_into(act[at[e]: at[e + 1]], self.w_down[e], y_sorted[at[e]: at[e + 1]])
         return ops.moe_gather(y_sorted, place, weights, not s.weight_on_input, add=shared)

@@ -59,6 +59,26 @@ CASE_B = {
 REL_ROWS_B = {0: 30, 2: 6}
 
 
+# key and value heads of one width (the tensor-core kernel for runs of new tokens takes these), windows
+# shorter than the prompts with and without kept tokens, a reader with a wider window than its owner
+CASE_C = {
+    "architecture": "Fesorax", "vocab": 150, "width": 96, "postln_alpha": 3.0, "norm": {"eps": 1e-6},
+    "embedding": {"scale": 8.0},
+    "layers": [
+        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 0.5, "bias_max": 100,
+                                        "mask": {"size": 70, "keep_first": 5}},
+         "mlp": {"kind": "moe", "router": {"experts": 4, "top": 1}, "expert": {"ff": 32, "limit": 1.5},
+                 "shared": {"ff": 32, "limit": 1.5}}},
+        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 0.3, "bias_max": 60,
+                                        "kv_from": 0, "mask": {"size": 100, "keep_first": 20}}, "mlp": None},
+        {"type": "attention", "mixer": {"heads": 1, "kv_heads": 1, "dim": 80, "vdim": 80, "scale": 0.4, "bias_max": 40,
+                                        "mask": {"size": 33, "keep_first": 0}},
+         "mlp": {"kind": "moe", "router": {"experts": 3, "top": 2}, "expert": {"ff": 16, "limit": 2.0}}},
+    ],
+}
+REL_ROWS_C = {0: 32, 1: 20, 2: 24}
+
+
 def tensor_shapes(cfg: dict, rel_rows: dict) -> dict:
     """Every tensor of the design by name, from the configuration alone."""
     W = cfg["width"]

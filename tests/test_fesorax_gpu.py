@@ -47,7 +47,7 @@ def test_norm_after_the_sum(cuda_device, width):
     assert np.abs(xd.cpu().numpy() - pf.rms_norm(2.5 * x.astype(np.float32).astype(np.float64), w, 1e-5)).max() < 1e-5 * np.abs(want).max()
 
 
-@pytest.mark.parametrize("H,d,dv", [(3, 8, 8), (1, 40, 136), (2, 100, 300)])
+@pytest.mark.parametrize("H,d,dv", [(3, 8, 8), (1, 40, 136), (2, 100, 300), (1, 160, 40)])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_mlstm_kernels_alone_and_carrying_their_state(cuda_device, H, d, dv, dtype):
     from bitnet_c_b200.csrc import ops
@@ -132,7 +132,7 @@ def test_mixture_of_experts_few_rows_and_many_rows(cuda_device, E, top, ff, shar
 
 
 # ---- whole models ------------------------------------------------------------------------------------
-CASES = {"A": (fc.CASE_A, fc.REL_ROWS_A), "B": (fc.CASE_B, fc.REL_ROWS_B)}
+CASES = {"A": (fc.CASE_A, fc.REL_ROWS_A), "B": (fc.CASE_B, fc.REL_ROWS_B), "C": (fc.CASE_C, fc.REL_ROWS_C)}
 
 
 @pytest.fixture(scope="module")
@@ -181,7 +181,7 @@ def _poison(cache):
         g.v.fill_(float("inf"))
 
 
-@pytest.mark.parametrize("case", ["A", "B"])
+@pytest.mark.parametrize("case", ["A", "B", "C"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_models_step_like_the_plain_statement_however_the_tokens_are_cut(folders, cuda_device, case, dtype):
     cfg = CASES[case][0]

@@ -59,11 +59,11 @@ def test_expert_clamps_gate_above_and_up_on_both_sides():
     assert np.allclose(y, [1.0 * s(1.0) * 2.0, -5.0 * s(-5.0) * 0.0, 0.5 * s(0.5) * 1.5])
 
 
-@pytest.mark.parametrize("case", ["A", "B"])
+@pytest.mark.parametrize("case", ["A", "B", "C"])
 def test_faults_in_the_mechanisms_move_the_logits_of_the_test_models(case):
     """The models of the engine tests are sharp enough: each of these faults moves some logit by far
     more than the engine's float32 tolerance, so a test that passes excludes them."""
-    cfg, rows = (fc.CASE_A, fc.REL_ROWS_A) if case == "A" else (fc.CASE_B, fc.REL_ROWS_B)
+    cfg, rows = {"A": (fc.CASE_A, fc.REL_ROWS_A), "B": (fc.CASE_B, fc.REL_ROWS_B), "C": (fc.CASE_C, fc.REL_ROWS_C)}[case]
     w = fc.draw_weights(cfg, rows, seed=5)
     toks = random_tokens(4, 150, cfg["vocab"])
     ref = pf.forward(cfg, w, toks)
