@@ -75,7 +75,16 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
 
   constexpr int VN = Vec16<T>::N;
   constexpr int MAX_D = 2;  // output dims per thread: v_dim <= 256
+  // Weighted sum of the values.  Rows of whole 16-byte pieces: a row is read by v_dim / VN threads,
+  // one piece each, and the rows of a chunk are shared out over the groups of such threads; the
+  // groups' sums meet in shared memory at the end.  Other widths: one thread per dimension.
+  const bool wide = (v_dim % VN) == 0 && v_dim / VN <= ATT_THREADS;
+  const int per_row = wide ? v_dim / VN : 1, groups = wide ? ATT_THREADS / per_row : 1;
+  const int piece = threadIdx.x % per_row, group = threadIdx.x / per_row;
   float acc[MAX_D] = {0.f, 0.f};
+  float accv[VN];
+#pragma unroll
+  for (int e = 0; e < VN; ++e) accv[e] = 0.f;
   float m_run = -INFINITY, l_run = 0.f;
 
   for (int base = 0; base < n_keys; base += ATT_CHUNK) {
@@ -107,18 +116,34 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
     float l_chunk = block_sum(p_mine, scratch);  // has the barrier that publishes ps[]
     l_run = l_run * alpha + l_chunk;
     m_run = m_new;
+    if (wide) {
 #pragma unroll
-    for (int r = 0; r < MAX_D; ++r) {
-      int d = threadIdx.x + r * ATT_THREADS;
-      if (d < v_dim) {
-        float a = acc[r] * alpha;
-        for (int j = 0; j < n; ++j) {
+      for (int e = 0; e < VN; ++e) accv[e] *= alpha;
+      if (group < groups) {
+        for (int j = group; j < n; j += groups) {
           int u = base + j;
           int p = u < n_first ? u : lo + (u - n_first);
-          const T* vrow = v_cache + cache_row_offset(pt, p, n_kv_heads, kvh, v_dim);
-          a = fmaf(ps[j], to_f32<T>(vrow[d]), a);
+          float vv[VN];
+          Vec16<T>::load(v_cache + cache_row_offset(pt, p, n_kv_heads, kvh, v_dim) + piece * VN, vv);
+          float w = ps[j];
+#pragma unroll
+          for (int e = 0; e < VN; ++e) accv[e] = fmaf(w, vv[e], accv[e]);
         }
-        acc[r] = a;
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < MAX_D; ++r) {
+        int d = threadIdx.x + r * ATT_THREADS;
+        if (d < v_dim) {
+          float a = acc[r] * alpha;
+          for (int j = 0; j < n; ++j) {
+            int u = base + j;
+            int p = u < n_first ? u : lo + (u - n_first);
+            const T* vrow = v_cache + cache_row_offset(pt, p, n_kv_heads, kvh, v_dim);
+            a = fmaf(ps[j], to_f32<T>(vrow[d]), a);
+          }
+          acc[r] = a;
+        }
       }
     }
     __syncthreads();  // ps[] is rewritten by the next chunk
@@ -126,6 +151,21 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
   float inv = 1.0f / l_run;
   if (gate) inv *= 1.0f / (1.0f + expf(-to_f32<T>(gate[(size_t)t * gate_stride + h])));
   T* orow = out + (size_t)t * out_stride + (size_t)h * v_dim;
+  if (wide) {
+    // groups * v_dim <= ATT_THREADS * VN floats, kept behind the scores
+    float* red = scratch + 32;
+    if (group < groups) {
+#pragma unroll
+      for (int e = 0; e < VN; ++e) red[(size_t)group * v_dim + piece * VN + e] = accv[e];
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < v_dim; d += ATT_THREADS) {
+      float a = 0.f;
+      for (int g = 0; g < groups; ++g) a += red[(size_t)g * v_dim + d];
+      orow[d] = from_f32<T>(a * inv);
+    }
+    return;
+  }
 #pragma unroll
   for (int r = 0; r < MAX_D; ++r) {
     int d = threadIdx.x + r * ATT_THREADS;
@@ -147,7 +187,7 @@ extern "C" int bn_attention_general_ex(const void* q, int q_stride, void* out, i
     return BN_ERR_BAD_ARG;
   if (n_heads > 65535) return BN_ERR_BAD_ARG;
   dim3 grid(n_tokens, n_heads);
-  size_t smem = (head_dim + ATT_CHUNK + 32) * sizeof(float);
+  size_t smem = (head_dim + ATT_CHUNK + 32 + ATT_THREADS * 8) * sizeof(float);  // q, scores, reduction scratch, the groups' sums
   if (dtype == BN_F32)
     BN_LAUNCH((attention_general_kernel<float>), grid, ATT_THREADS, smem, stream, 
         (const float*)q, q_stride, (float*)out, out_stride, n_heads, n_kv_heads, head_dim, v_dim, scale, window,

@@ -168,6 +168,71 @@ __device__ __forceinline__ float warp_dot(const float* __restrict__ xs, const fl
   return acc;
 }
 
+// R such dot products at once, of the same numbers with R rows that lie `stride` elements apart: the rows'
+// loads are in flight together (a row alone leaves the memory waiting between its few loads).
+template <int R>
+__device__ __forceinline__ void warp_dot_rows(const float* __restrict__ xs, const __nv_bfloat16* __restrict__ w, size_t stride,
+                                              int n, int lane, float* out) {
+  float acc[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) acc[r] = 0.f;
+  if ((n & 7) == 0 && (stride & 7) == 0 && (((uintptr_t)w) & 15) == 0) {
+    for (int c = lane * 8; c < n; c += 256) {
+      uint4 raw[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r) raw[r] = *reinterpret_cast<const uint4*>(w + r * stride + c);
+      float4 x0 = *reinterpret_cast<const float4*>(xs + c), x1 = *reinterpret_cast<const float4*>(xs + c + 4);
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[r]);
+        float2 a = __bfloat1622float2(h2[0]), b = __bfloat1622float2(h2[1]), cc = __bfloat1622float2(h2[2]), d = __bfloat1622float2(h2[3]);
+        acc[r] = fmaf(x0.x, a.x, acc[r]); acc[r] = fmaf(x0.y, a.y, acc[r]);
+        acc[r] = fmaf(x0.z, b.x, acc[r]); acc[r] = fmaf(x0.w, b.y, acc[r]);
+        acc[r] = fmaf(x1.x, cc.x, acc[r]); acc[r] = fmaf(x1.y, cc.y, acc[r]);
+        acc[r] = fmaf(x1.z, d.x, acc[r]); acc[r] = fmaf(x1.w, d.y, acc[r]);
+      }
+    }
+  } else {
+    for (int c = lane; c < n; c += 32)
+#pragma unroll
+      for (int r = 0; r < R; ++r) acc[r] = fmaf(xs[c], __bfloat162float(w[r * stride + c]), acc[r]);
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], o);
+    out[r] = acc[r];
+  }
+}
+template <int R>
+__device__ __forceinline__ void warp_dot_rows(const float* __restrict__ xs, const float* __restrict__ w, size_t stride, int n,
+                                              int lane, float* out) {
+  float acc[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) acc[r] = 0.f;
+  if ((n & 3) == 0 && (stride & 3) == 0 && (((uintptr_t)w) & 15) == 0) {
+    for (int c = lane * 4; c < n; c += 128) {
+      float4 x = *reinterpret_cast<const float4*>(xs + c);
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        float4 f = *reinterpret_cast<const float4*>(w + r * stride + c);
+        acc[r] = fmaf(x.x, f.x, acc[r]); acc[r] = fmaf(x.y, f.y, acc[r]);
+        acc[r] = fmaf(x.z, f.z, acc[r]); acc[r] = fmaf(x.w, f.w, acc[r]);
+      }
+    }
+  } else {
+    for (int c = lane; c < n; c += 32)
+#pragma unroll
+      for (int r = 0; r < R; ++r) acc[r] = fmaf(xs[c], w[r * stride + c], acc[r]);
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], o);
+    out[r] = acc[r];
+  }
+}
+
 // Block-wide sum for blocks of up to 1024 threads; `scratch` holds 32 floats.
 // Every thread gets the result.  The order of additions depends only on the
 // block size, never on what else runs, so a row's result does not change with

@@ -26,7 +26,7 @@ __global__ void mlstm_gates_kernel(const T* __restrict__ h, int width, const W* 
                                    const W* __restrict__ bias, int n_heads, float cap, float* __restrict__ gates) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float xs[];  // width
+  extern __shared__ __align__(16) float xs[];  // width
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
   const T* row = h + (size_t)t * width;
@@ -190,16 +190,16 @@ __global__ void __launch_bounds__(32) mlstm_recurrence_warp_kernel(
     nq = warp_sum(nq);
     float denom = fmaxf(fabsf(nq), expf(-m)) + 1e-6f;
     __syncwarp();
-    float bv = b * v, acc = 0.f;
+    float bv = b * v, acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;  // four chains, so that the sums do not wait for one another
 #pragma unroll
     for (int d4 = 0; d4 < D; d4 += 4) {
       float4 k4 = *reinterpret_cast<const float4*>(sk + d4), q4 = *reinterpret_cast<const float4*>(sq + d4);
-      S[d4] = fmaf(a, S[d4], bv * k4.x);         acc = fmaf(S[d4], q4.x, acc);
-      S[d4 + 1] = fmaf(a, S[d4 + 1], bv * k4.y); acc = fmaf(S[d4 + 1], q4.y, acc);
-      S[d4 + 2] = fmaf(a, S[d4 + 2], bv * k4.z); acc = fmaf(S[d4 + 2], q4.z, acc);
-      S[d4 + 3] = fmaf(a, S[d4 + 3], bv * k4.w); acc = fmaf(S[d4 + 3], q4.w, acc);
+      S[d4] = fmaf(a, S[d4], bv * k4.x);         acc0 = fmaf(S[d4], q4.x, acc0);
+      S[d4 + 1] = fmaf(a, S[d4 + 1], bv * k4.y); acc1 = fmaf(S[d4 + 1], q4.y, acc1);
+      S[d4 + 2] = fmaf(a, S[d4 + 2], bv * k4.z); acc2 = fmaf(S[d4 + 2], q4.z, acc2);
+      S[d4 + 3] = fmaf(a, S[d4 + 3], bv * k4.w); acc3 = fmaf(S[d4 + 3], q4.w, acc3);
     }
-    if (has_col) out[(size_t)t * n_heads * vdim + (size_t)head * vdim + c] = acc / denom;
+    if (has_col) out[(size_t)t * n_heads * vdim + (size_t)head * vdim + c] = ((acc0 + acc1) + (acc2 + acc3)) / denom;
   }
   if (has_col) {
 #pragma unroll

@@ -27,7 +27,7 @@ __global__ void moe_route_kernel(const T* __restrict__ h, int width, const W* __
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float z[MOE_MAX_EXPERTS];
-  extern __shared__ float xs[];  // width
+  extern __shared__ __align__(16) float xs[];  // width
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
   const T* row = h + (size_t)t * width;
@@ -99,7 +99,7 @@ __global__ void moe_gate_up_kernel(const T* __restrict__ h, int width, const int
                                    float slope, T* __restrict__ y) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float xs[];  // width
+  extern __shared__ __align__(16) float xs[];  // width
   const int item = blockIdx.x, t = item / top;
   const int e = ids[item];
   const float wt = scale_input ? weights[item] : 1.0f;
@@ -109,14 +109,27 @@ __global__ void moe_gate_up_kernel(const T* __restrict__ h, int width, const int
     xs[c] = to_f32<T>(from_f32<T>(to_f32<T>(h[(size_t)t * width + c]) * wt));
   __syncthreads();
   const int j0 = blockIdx.y * MOE_ROWS_PER_BLOCK, j1 = min(ff, j0 + MOE_ROWS_PER_BLOCK);
-  for (int j = j0 + warp; j < j1; j += n_warps) {
-    float g = warp_dot(xs, w_gate + (size_t)e * expert_stride + (size_t)j * width, width, lane);
-    float u = warp_dot(xs, w_up + (size_t)e * expert_stride + (size_t)j * width, width, lane);
-    if (lane == 0) {
+  // a warp takes four neighbouring rows of both matrices at a time
+  for (int j = j0 + warp * 4; j < j1; j += n_warps * 4) {
+    float g4[4], u4[4];
+    const T* gr = w_gate + (size_t)e * expert_stride + (size_t)j * width;
+    const T* ur = w_up + (size_t)e * expert_stride + (size_t)j * width;
+    if (j + 4 <= j1) {
+      warp_dot_rows<4>(xs, gr, (size_t)width, width, lane, g4);
+      warp_dot_rows<4>(xs, ur, (size_t)width, width, lane, u4);
+    } else {
+      for (int r = 0; r < j1 - j; ++r) {
+        g4[r] = warp_dot(xs, gr + (size_t)r * width, width, lane);
+        u4[r] = warp_dot(xs, ur + (size_t)r * width, width, lane);
+      }
+    }
+    if (lane < 4 && j + lane < j1) {
       // the products' results pass through the compute type, as they do on the sorted path
+      float g = lane == 0 ? g4[0] : lane == 1 ? g4[1] : lane == 2 ? g4[2] : g4[3];
+      float u = lane == 0 ? u4[0] : lane == 1 ? u4[1] : lane == 2 ? u4[2] : u4[3];
       g = fminf(to_f32<T>(from_f32<T>(g)), limit);
       u = fminf(fmaxf(to_f32<T>(from_f32<T>(u)), -limit), limit);
-      y[(size_t)item * ff + j] = from_f32<T>(g / (1.0f + expf(-slope * g)) * (u + 1.0f));
+      y[(size_t)item * ff + j + lane] = from_f32<T>(g / (1.0f + expf(-slope * g)) * (u + 1.0f));
     }
   }
 }
@@ -128,22 +141,31 @@ __global__ void moe_down_kernel(const T* __restrict__ y, int ff, const int* __re
                                 int width, int top, const void* __restrict__ add, int add_dtype, float* __restrict__ out) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float ys[];  // top * ff: the token's activations, expert by expert
+  extern __shared__ __align__(16) float ys[];  // top * ff: the token's activations, expert by expert
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
   for (int i = threadIdx.x; i < top * ff; i += blockDim.x) ys[i] = to_f32<T>(y[(size_t)t * top * ff + i]);
   __syncthreads();
   const int c0 = blockIdx.y * MOE_ROWS_PER_BLOCK, c1 = min(width, c0 + MOE_ROWS_PER_BLOCK);
-  for (int c = c0 + warp; c < c1; c += n_warps) {
-    float total = 0.f;
+  for (int c = c0 + warp * 4; c < c1; c += n_warps * 4) {
+    float total[4] = {0.f, 0.f, 0.f, 0.f};
     for (int k = 0; k < top; ++k) {
       const int e = ids[(size_t)t * top + k];
-      float dot = warp_dot(ys + (size_t)k * ff, w_down + ((size_t)e * width + c) * ff, ff, lane);
-      total += scale_output ? dot * weights[(size_t)t * top + k] : dot;
+      const T* wr = w_down + ((size_t)e * width + c) * ff;
+      float d4[4] = {0.f, 0.f, 0.f, 0.f};
+      if (c + 4 <= c1) {
+        warp_dot_rows<4>(ys + (size_t)k * ff, wr, (size_t)ff, ff, lane, d4);
+      } else {
+        for (int r = 0; r < c1 - c; ++r) d4[r] = warp_dot(ys + (size_t)k * ff, wr + (size_t)r * ff, ff, lane);
+      }
+      const float wt = scale_output ? weights[(size_t)t * top + k] : 1.0f;
+#pragma unroll
+      for (int r = 0; r < 4; ++r) total[r] += d4[r] * wt;
     }
-    if (lane == 0) {
-      if (add) total += load_as_f32(add, add_dtype, (size_t)t * width + c);
-      out[(size_t)t * width + c] = total;
+    if (lane < 4 && c + lane < c1) {
+      float v = lane == 0 ? total[0] : lane == 1 ? total[1] : lane == 2 ? total[2] : total[3];
+      if (add) v += load_as_f32(add, add_dtype, (size_t)t * width + c + lane);
+      out[(size_t)t * width + c + lane] = v;
     }
   }
 }
@@ -198,8 +220,9 @@ __global__ void moe_count_kernel(const int* __restrict__ ids, int n_items, int* 
   if (i < n_items) atomicAdd(&counts[ids[i]], 1);
 }
 
-// offsets[e] = first row of expert e in the sorted order (offsets[n_experts] = n_items); one block.
-__global__ void moe_offsets_kernel(const int* __restrict__ counts, int n_experts, int* __restrict__ offsets,
+// offsets[e] = first row of expert e in the sorted order: the experts' rows packed one behind another
+// (cap == 0; offsets[n_experts] = n_items), or every expert in a block of cap rows of its own; one block.
+__global__ void moe_offsets_kernel(const int* __restrict__ counts, int n_experts, int cap, int* __restrict__ offsets,
                                    int* __restrict__ cursor) {
   pdl_launch_dependents();
   pdl_wait();
@@ -208,7 +231,7 @@ __global__ void moe_offsets_kernel(const int* __restrict__ counts, int n_experts
     for (int e = 0; e < n_experts; ++e) {
       offsets[e] = at;
       cursor[e] = at;
-      at += counts[e];
+      at += cap > 0 ? cap : counts[e];
     }
     offsets[n_experts] = at;
   }
@@ -253,17 +276,26 @@ __global__ void moe_gather_kernel(const T* __restrict__ y_sorted, int width, con
   }
 }
 
-// counts: [n_experts] zeroed by the caller; offsets: [n_experts + 1]; cursor: [n_experts]; place: [n_items]
-extern "C" int bn_moe_sort(const void* h, int dtype, int n_tokens, int width, const int* ids, const float* weights,
-                           int scale_input, int top, int n_experts, int* counts, int* offsets, int* cursor, int* place,
-                           void* x_sorted, cudaStream_t stream) {
+// counts: [n_experts], zeroed by the caller: how many (token, expert) items chose each expert
+extern "C" int bn_moe_count(const int* ids, int n_items, int* counts, cudaStream_t stream) {
+  if (n_items <= 0) return BN_OK;
+  if (!ids || !counts) return BN_ERR_BAD_ARG;
+  BN_LAUNCH(moe_count_kernel, (n_items + 255) / 256, 256, 0, stream, ids, n_items, counts);
+  BN_CHECK_LAUNCH();
+  return BN_OK;
+}
+
+// counts as bn_moe_count left them; offsets: [n_experts + 1]; cursor: [n_experts]; place: [n_items];
+// x_sorted: [n_items, width] (cap == 0) or [n_experts * cap, width] (cap >= the largest count)
+extern "C" int bn_moe_scatter(const void* h, int dtype, int n_tokens, int width, const int* ids, const float* weights,
+                              int scale_input, int top, int n_experts, int cap, const int* counts, int* offsets,
+                              int* cursor, int* place, void* x_sorted, cudaStream_t stream) {
   if (n_tokens <= 0) return BN_OK;
   if (!h || !ids || !weights || !counts || !offsets || !cursor || !place || !x_sorted || width <= 0 || top <= 0 ||
-      n_experts <= 0)
+      n_experts <= 0 || cap < 0)
     return BN_ERR_BAD_ARG;
   int n_items = n_tokens * top;
-  BN_LAUNCH(moe_count_kernel, (n_items + 255) / 256, 256, 0, stream, ids, n_items, counts);
-  BN_LAUNCH(moe_offsets_kernel, 1, 32, 0, stream, (const int*)counts, n_experts, offsets, cursor);
+  BN_LAUNCH(moe_offsets_kernel, 1, 32, 0, stream, counts, n_experts, cap, offsets, cursor);
   if (dtype == BN_F32)
     BN_LAUNCH(moe_scatter_kernel<float>, n_items, 128, 0, stream, (const float*)h, width, ids, weights, scale_input, top,
               cursor, place, (float*)x_sorted);

@@ -1105,24 +1105,37 @@ def moe_experts_few(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w
     return out
 
 
-def moe_sort(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, n_experts: int, scale_input: bool):
-    """Sort the (token, expert) items by expert: ``(x_sorted [T * top, width], place int32 [T * top],
-    offsets int32 [experts + 1])``; rows ``offsets[e] .. offsets[e + 1]`` of ``x_sorted`` are the inputs of expert
-    e (times their weight with ``scale_input``), and item i went to row ``place[i]``."""
+def moe_count(ids: torch.Tensor, n_experts: int) -> torch.Tensor:
+    """int32 ``[experts]``: how many (token, expert) items chose each expert."""
+    _need(ids, "ids", torch.int32, 2)
+    counts = torch.zeros(n_experts, dtype=torch.int32, device=ids.device)
+    _check(_fn("moe", "bn_moe_count")(_ptr(ids), int(ids.numel()), _ptr(counts), _stream()), "moe_count")
+    return counts
+
+
+def moe_sort(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, counts: torch.Tensor, scale_input: bool,
+             cap: int = 0):
+    """Sort the (token, expert) items by expert: ``(x_sorted, place int32 [T * top], offsets int32 [experts + 1])``.
+    Item i went to row ``place[i]`` of ``x_sorted``, which holds its token's row of h (times its weight with
+    ``scale_input``).  ``cap`` = 0: the experts' rows are packed, expert e's are rows ``offsets[e] ..
+    offsets[e + 1]`` of ``[T * top, width]``.  ``cap`` > 0 (at least the largest of ``counts``): expert e's rows
+    begin at ``e * cap`` of ``[experts * cap, width]``; rows that no item took hold nothing."""
     _need(h, "h", dims=2)
     _need(ids, "ids", torch.int32, 2)
     _need(weights, "weights", torch.float32, 2)
+    _need(counts, "counts", torch.int32, 1)
     T, width = h.shape
-    top = ids.shape[1]
-    book = torch.zeros(3 * n_experts + 1, dtype=torch.int32, device=h.device)
-    counts, offsets, cursor = book[:n_experts], book[n_experts:2 * n_experts + 1], book[2 * n_experts + 1:]
+    top, n_experts = ids.shape[1], counts.shape[0]
+    book = torch.empty(2 * n_experts + 1, dtype=torch.int32, device=h.device)
+    offsets, cursor = book[:n_experts + 1], book[n_experts + 1:]
     place = torch.empty(T * top, dtype=torch.int32, device=h.device)
-    x_sorted = torch.empty((T * top, width), dtype=h.dtype, device=h.device)
-    _check(_fn("moe", "bn_moe_sort")(_ptr(h), int(_code(h)), int(T), int(width), _ptr(ids), _ptr(weights),
-                                     int(bool(scale_input)), int(top), int(n_experts), _ptr(counts), _ptr(offsets),
-                                     _ptr(cursor), _ptr(place), _ptr(x_sorted), _stream()), "moe_sort")
+    rows = n_experts * cap if cap > 0 else T * top
+    x_sorted = torch.empty((rows, width), dtype=h.dtype, device=h.device)
+    _check(_fn("moe", "bn_moe_scatter")(_ptr(h), int(_code(h)), int(T), int(width), _ptr(ids), _ptr(weights),
+                                        int(bool(scale_input)), int(top), int(n_experts), int(cap), _ptr(counts),
+                                        _ptr(offsets), _ptr(cursor), _ptr(place), _ptr(x_sorted), _stream()), "moe_sort")
     global LAUNCHES
-    LAUNCHES += 2
+    LAUNCHES += 1
     return x_sorted, place, offsets
 
 
@@ -1135,7 +1148,7 @@ def moe_gather(y_sorted: torch.Tensor, place: torch.Tensor, weights: torch.Tenso
     _need(weights, "weights", torch.float32, 2)
     T, top = weights.shape
     width = y_sorted.shape[1]
-    if y_sorted.shape[0] != T * top or place.shape[0] != T * top:
+    if y_sorted.shape[0] < T * top or place.shape[0] != T * top:
         raise KernelError("moe_gather: sizes do not fit")
     if add is not None:
         _need(add, "add", dims=2)
@@ -1146,6 +1159,19 @@ def moe_gather(y_sorted: torch.Tensor, place: torch.Tensor, weights: torch.Tenso
                                        int(bool(scale_output)), int(top), _ptr(add), int(_code(add) if add is not None else 0),
                                        _ptr(out), _stream()), "moe_gather")
     return out
+
+
+def batched_matmul(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``[B, M, K] . [B, N, K]^T -> [B, M, N]`` by the library's batched product (float32 sums; float32 inputs
+    in true float32): the experts of a mixture at once, each on its own block of rows."""
+    _need(x, "x", dims=3)
+    _need(w, "w", x.dtype, 3)
+    if x.shape[0] != w.shape[0] or x.shape[2] != w.shape[2]:
+        raise KernelError(f"batched_matmul: x {tuple(x.shape)} and w {tuple(w.shape)} do not fit")
+    if w.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
+        raise KernelError("float32 products need torch.backends.cuda.matmul.allow_tf32 = False")
+    product = lambda: torch.bmm(x, w.transpose(1, 2))
+    return product() if PROFILE is None else _timed("library.bmm", product)
 
 
 def matmul_into(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:

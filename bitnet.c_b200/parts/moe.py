@@ -25,6 +25,7 @@ class Moe(FeedForward):
     kernels = ("linear", "linear_mma", "linear_tc", "gemm_tc", "act", "moe")
     graph_safe = True  # the steps that are recorded are decode steps, which take the path without the host
     FEW_ITEMS = 64  # up to so many (token, expert) items the streaming kernels run
+    PAD_FACTOR = 2.0  # blocks of equal size for all experts while they hold at most so many times the rows used
 
     def params(self) -> Dict[str, ParamSpec]:
         s = self.spec
@@ -67,10 +68,24 @@ class Moe(FeedForward):
         if ctx.decode or T * s.top <= self.FEW_ITEMS:
             return ops.moe_experts_few(h, ids, weights, self.w_gate_up, self.w_down, s.expert_limit, s.slope,
                                        s.weight_on_input, add=shared)
-        x_sorted, place, offsets = ops.moe_sort(h, ids, weights, s.n_experts, s.weight_on_input)
-        at = offsets.cpu().tolist()
+        counts = ops.moe_count(ids, s.n_experts)
+        per_expert = counts.cpu().tolist()  # the one place where the host waits for the device
         dt, dev_ = self.build.dtype, h.device
-        # every expert's rows lie side by side: its two products write into slices, the activation runs once
+        cap = -(-max(per_expert) // 8) * 8
+        if cap * s.n_experts <= self.PAD_FACTOR * T * s.top:
+            # the experts are about evenly used: each gets a block of ``cap`` rows, and all of them run as
+            # one batched product each way (rows that no token took compute nothing that is read)
+            x_pad, place, _ = ops.moe_sort(h, ids, weights, counts, s.weight_on_input, cap=cap)
+            gate_up = ops.batched_matmul(x_pad.view(s.n_experts, cap, s.width), self.w_gate_up)
+            act = torch.empty((s.n_experts * cap, s.expert_ff), dtype=dt, device=dev_)
+            ops.glu_limited(gate_up.view(s.n_experts * cap, 2 * s.expert_ff), act, s.expert_limit, s.slope)
+            y_pad = ops.batched_matmul(act.view(s.n_experts, cap, s.expert_ff), self.w_down)
+            return ops.moe_gather(y_pad.view(s.n_experts * cap, s.width), place, weights, not s.weight_on_input, add=shared)
+        # uneven: the experts' rows packed side by side, their products one after another into slices
+        x_sorted, place, _ = ops.moe_sort(h, ids, weights, counts, s.weight_on_input)
+        at = [0]
+        for c in per_expert:
+            at.append(at[-1] + c)
         gate_up = torch.empty((T * s.top, 2 * s.expert_ff), dtype=dt, device=dev_)
         for e in range(s.n_experts):
             if at[e + 1] > at[e]:
