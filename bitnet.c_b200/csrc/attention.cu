@@ -53,7 +53,8 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
                                          const int* __restrict__ tok_seq,
                                          const int* __restrict__ tok_pos, const int* __restrict__ slots,
                                          const int* __restrict__ page_table, int pt_stride,
-                                         const T* __restrict__ k_cache, const T* __restrict__ v_cache) {
+                                         const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                                         float* __restrict__ part, int n_splits) {
   pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
   pdl_wait();               // the kernels before this one have completed and their writes are visible
   extern __shared__ float sm[];
@@ -87,7 +88,9 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
   for (int e = 0; e < VN; ++e) accv[e] = 0.f;
   float m_run = -INFINITY, l_run = 0.f;
 
-  for (int base = 0; base < n_keys; base += ATT_CHUNK) {
+  // with n_splits > 1 the chunks of keys are dealt out to the blocks blockIdx.z = 0 .. n_splits - 1, which
+  // leave their running maximum, sum and unnormalised output in `part` for attention_merge_kernel
+  for (int base = blockIdx.z * ATT_CHUNK; base < n_keys; base += ATT_CHUNK * n_splits) {
     int n = min(ATT_CHUNK, n_keys - base);
     float s = -INFINITY;
     if ((int)threadIdx.x < n) {
@@ -151,6 +154,8 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
   float inv = 1.0f / l_run;
   if (gate) inv *= 1.0f / (1.0f + expf(-to_f32<T>(gate[(size_t)t * gate_stride + h])));
   T* orow = out + (size_t)t * out_stride + (size_t)h * v_dim;
+  float* prow = part ? part + (((size_t)t * n_heads + h) * n_splits + blockIdx.z) * (v_dim + 2) : nullptr;
+  if (prow && threadIdx.x == 0) { prow[0] = m_run; prow[1] = l_run; }
   if (wide) {
     // groups * v_dim <= ATT_THREADS * VN floats, kept behind the scores
     float* red = scratch + 32;
@@ -162,14 +167,45 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
     for (int d = threadIdx.x; d < v_dim; d += ATT_THREADS) {
       float a = 0.f;
       for (int g = 0; g < groups; ++g) a += red[(size_t)g * v_dim + d];
-      orow[d] = from_f32<T>(a * inv);
+      if (prow) prow[2 + d] = a;
+      else orow[d] = from_f32<T>(a * inv);
     }
     return;
   }
 #pragma unroll
   for (int r = 0; r < MAX_D; ++r) {
     int d = threadIdx.x + r * ATT_THREADS;
-    if (d < v_dim) orow[d] = from_f32<T>(acc[r] * inv);
+    if (d < v_dim) {
+      if (prow) prow[2 + d] = acc[r];
+      else orow[d] = from_f32<T>(acc[r] * inv);
+    }
+  }
+}
+
+// out[t][h] = sum_z e^{m_z - M} acc_z / sum_z e^{m_z - M} l_z (times the logistic function of the gate), M = max_z m_z
+template <typename T>
+__global__ void attention_merge_kernel(const float* __restrict__ part, int n_splits, int n_heads, int v_dim,
+                                       const T* __restrict__ gate, int gate_stride, T* __restrict__ out, int out_stride) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, h = blockIdx.y;
+  const float* p = part + ((size_t)t * n_heads + h) * n_splits * (v_dim + 2);
+  float M = -INFINITY;
+  for (int z = 0; z < n_splits; ++z) M = fmaxf(M, p[(size_t)z * (v_dim + 2)]);
+  float L = 0.f;
+  for (int z = 0; z < n_splits; ++z) {
+    float m = p[(size_t)z * (v_dim + 2)];
+    if (m != -INFINITY) L += expf(m - M) * p[(size_t)z * (v_dim + 2) + 1];
+  }
+  float inv = 1.0f / L;
+  if (gate) inv *= 1.0f / (1.0f + expf(-to_f32<T>(gate[(size_t)t * gate_stride + h])));
+  for (int d = threadIdx.x; d < v_dim; d += blockDim.x) {
+    float a = 0.f;
+    for (int z = 0; z < n_splits; ++z) {
+      float m = p[(size_t)z * (v_dim + 2)];
+      if (m != -INFINITY) a = fmaf(expf(m - M), p[(size_t)z * (v_dim + 2) + 2 + d], a);
+    }
+    out[(size_t)t * out_stride + (size_t)h * v_dim + d] = from_f32<T>(a * inv);
   }
 }
 
@@ -180,27 +216,39 @@ extern "C" int bn_attention_general_ex(const void* q, int q_stride, void* out, i
                                        int window, int keep_first, const float* rel, int n_rel, const void* gate,
                                        int gate_stride, const int* tok_seq, const int* tok_pos, const int* slots,
                                        const int* page_table, int pt_stride,
-                                       const void* k_cache, const void* v_cache, cudaStream_t stream) {
+                                       const void* k_cache, const void* v_cache, float* part, int n_splits,
+                                       cudaStream_t stream) {
   if (n_tokens <= 0) return BN_OK;
+  if (n_splits < 1 || n_splits > 64 || (n_splits > 1 && !part)) return BN_ERR_BAD_ARG;
+  if (n_splits == 1) part = nullptr;
   if (head_dim <= 0 || head_dim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads ||
       window < 0 || keep_first < 0 || v_dim <= 0 || v_dim > 256 || (rel && n_rel <= 0))
     return BN_ERR_BAD_ARG;
   if (n_heads > 65535) return BN_ERR_BAD_ARG;
-  dim3 grid(n_tokens, n_heads);
+  dim3 grid(n_tokens, n_heads, n_splits);
   size_t smem = (head_dim + ATT_CHUNK + 32 + ATT_THREADS * 8) * sizeof(float);  // q, scores, reduction scratch, the groups' sums
   if (dtype == BN_F32)
     BN_LAUNCH((attention_general_kernel<float>), grid, ATT_THREADS, smem, stream, 
         (const float*)q, q_stride, (float*)out, out_stride, n_heads, n_kv_heads, head_dim, v_dim, scale, window,
         keep_first, rel, n_rel, (const float*)gate, gate_stride,
-        tok_seq, tok_pos, slots, page_table, pt_stride, (const float*)k_cache, (const float*)v_cache);
+        tok_seq, tok_pos, slots, page_table, pt_stride, (const float*)k_cache, (const float*)v_cache, part, n_splits);
   else if (dtype == BN_BF16)
     BN_LAUNCH((attention_general_kernel<__nv_bfloat16>), grid, ATT_THREADS, smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, head_dim, v_dim,
         scale, window, keep_first, rel, n_rel, (const __nv_bfloat16*)gate, gate_stride,
         tok_seq, tok_pos, slots, page_table, pt_stride,
-        (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache);
+        (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, part, n_splits);
   else
     return BN_ERR_BAD_ARG;
+  if (part) {
+    dim3 mgrid(n_tokens, n_heads);
+    if (dtype == BN_F32)
+      BN_LAUNCH((attention_merge_kernel<float>), mgrid, 128, 0, stream, (const float*)part, n_splits, n_heads, v_dim,
+                (const float*)gate, gate_stride, (float*)out, out_stride);
+    else
+      BN_LAUNCH((attention_merge_kernel<__nv_bfloat16>), mgrid, 128, 0, stream, (const float*)part, n_splits, n_heads, v_dim,
+                (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, out_stride);
+  }
   BN_CHECK_LAUNCH();
   return BN_OK;
 }
@@ -212,5 +260,5 @@ extern "C" int bn_attention_general(const void* q, int q_stride, void* out, int 
                                     const void* k_cache, const void* v_cache, cudaStream_t stream) {
   return bn_attention_general_ex(q, q_stride, out, out_stride, dtype, n_tokens, n_heads, n_kv_heads, head_dim, head_dim,
                                  scale, window, 0, nullptr, 0, nullptr, 0, tok_seq, tok_pos, slots, page_table,
-                                 pt_stride, k_cache, v_cache, stream);
+                                 pt_stride, k_cache, v_cache, nullptr, 1, stream);
 }

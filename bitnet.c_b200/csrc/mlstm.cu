@@ -127,90 +127,86 @@ __global__ void mlstm_recurrence_kernel(const T* __restrict__ qkv, int row_strid
   }
 }
 
-// Head sizes up to 128: one warp per (sequence, head, 32 value columns), the lane's column of S in
-// registers (D of them, dim padded with zeros), n spread over the lanes, q and k of the token handed
-// round through shared memory.  No barrier but the warp's own; the next token's row is requested
-// while this one's is worked on.  The arithmetic is that of the kernel above, term by term.
+// Head sizes up to 128: a block of four warps per (sequence, head, 32 value columns).  Each warp keeps a
+// quarter of the rows of S for the block's 32 columns in registers (one column per lane, D / 4 rows, dim
+// padded with zeros to D), its rows' share of n spread over its lanes, and hands its rows of q and k
+// round through shared memory of its own.  Per token the warps' partial sums of S^T q and n . q meet in
+// shared memory behind one barrier (two sets of buffers in turn); warp 0 adds them, always in the same
+// order, and stores.  The next token's row is requested while this one's is worked on.
 template <typename T, int D>
-__global__ void __launch_bounds__(32) mlstm_recurrence_warp_kernel(
+__global__ void __launch_bounds__(128) mlstm_recurrence_warp_kernel(
     const T* __restrict__ qkv, int row_stride, int k_off, int v_off, const float* __restrict__ gates,
     float* __restrict__ state, const int* __restrict__ seq_start, const int* __restrict__ slots, int n_heads, int dim,
     int vdim, float q_scale, float* __restrict__ out) {
   pdl_launch_dependents();
   pdl_wait();
-  constexpr int R = D / 32;
-  __shared__ __align__(16) float sq[D], sk[D];
-  const int seq = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
+  constexpr int DW = D / 4;  // rows of S per warp: 8, 16 or 32
+  __shared__ __align__(16) float sq[4][DW], sk[4][DW];
+  __shared__ float part_o[2][4][32], part_nq[2][4];
+  const int seq = blockIdx.x, head = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int c = blockIdx.z * 32 + lane;
   const bool has_col = c < vdim;
+  const int d0 = warp * DW;           // this warp's first row
+  const int my_d = d0 + lane;         // the row whose q, k and n this lane holds (lanes below DW)
+  const bool has_row = lane < DW && my_d < dim;
   const size_t per_head = (size_t)dim * vdim + dim + 1;
   float* st = state + ((size_t)slots[seq] * n_heads + head) * per_head;
   float* st_n = st + (size_t)dim * vdim;
-  float S[D];
+  float S[DW];
 #pragma unroll
-  for (int d = 0; d < D; ++d) S[d] = (has_col && d < dim) ? st[(size_t)d * vdim + c] : 0.f;
-  float n[R];
-#pragma unroll
-  for (int r = 0; r < R; ++r) n[r] = (lane + 32 * r < dim) ? st_n[lane + 32 * r] : 0.f;
+  for (int r = 0; r < DW; ++r) S[r] = (has_col && d0 + r < dim) ? st[(size_t)(d0 + r) * vdim + c] : 0.f;
+  float n = has_row ? st_n[my_d] : 0.f;
   float m = st_n[dim];
   const int t0 = seq_start[seq], t1 = seq_start[seq + 1];
-  float qn[R], kn[R], vn = 0.f, gi_n = 0.f, gf_n = 0.f;
+  float qn = 0.f, kn = 0.f, vn = 0.f, gi_n = 0.f, gf_n = 0.f;
   auto fetch = [&](int t) {
     const T* row = qkv + (size_t)t * row_stride;
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      int d = lane + 32 * r;
-      qn[r] = d < dim ? to_f32<T>(row[(size_t)head * dim + d]) * q_scale : 0.f;
-      kn[r] = d < dim ? to_f32<T>(row[k_off + (size_t)head * dim + d]) : 0.f;
-    }
+    qn = has_row ? to_f32<T>(row[(size_t)head * dim + my_d]) * q_scale : 0.f;
+    kn = has_row ? to_f32<T>(row[k_off + (size_t)head * dim + my_d]) : 0.f;
     vn = has_col ? to_f32<T>(row[v_off + (size_t)head * vdim + c]) : 0.f;
     gi_n = gates[(size_t)t * 2 * n_heads + head];
     gf_n = gates[(size_t)t * 2 * n_heads + n_heads + head];
   };
   if (t0 < t1) fetch(t0);
   for (int t = t0; t < t1; ++t) {
-    float q[R], k[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) { q[r] = qn[r]; k[r] = kn[r]; }
-    const float v = vn, gi = gi_n, gf = gf_n;
-    __syncwarp();  // the step before has read sq, sk
-#pragma unroll
-    for (int r = 0; r < R; ++r) { sq[lane + 32 * r] = q[r]; sk[lane + 32 * r] = k[r]; }
+    const float q = qn, k = kn, v = vn, gi = gi_n, gf = gf_n;
+    const int buf = (t - t0) & 1;
+    __syncwarp();  // the step before has read this warp's sq, sk
+    if (lane < DW) { sq[warp][lane] = q; sk[warp][lane] = k; }
     if (t + 1 < t1) fetch(t + 1);
     float m_new = fmaxf(gf + m, gi);
     float a = expf(gf + m - m_new), b = expf(gi - m_new);
     m = m_new;
-    float nq = 0.f;
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      n[r] = a * n[r] + b * k[r];
-      nq = fmaf(n[r], q[r], nq);
-    }
-    // the same order of additions as the kernel above: lane l adds its d = l, l + 32, ..., then the lanes meet
-    nq = warp_sum(nq);
-    float denom = fmaxf(fabsf(nq), expf(-m)) + 1e-6f;
+    n = a * n + b * k;
+    float nq = warp_sum(n * q);
     __syncwarp();
-    float bv = b * v, acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;  // four chains, so that the sums do not wait for one another
+    float bv = b * v, acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
 #pragma unroll
-    for (int d4 = 0; d4 < D; d4 += 4) {
-      float4 k4 = *reinterpret_cast<const float4*>(sk + d4), q4 = *reinterpret_cast<const float4*>(sq + d4);
-      S[d4] = fmaf(a, S[d4], bv * k4.x);         acc0 = fmaf(S[d4], q4.x, acc0);
-      S[d4 + 1] = fmaf(a, S[d4 + 1], bv * k4.y); acc1 = fmaf(S[d4 + 1], q4.y, acc1);
-      S[d4 + 2] = fmaf(a, S[d4 + 2], bv * k4.z); acc2 = fmaf(S[d4 + 2], q4.z, acc2);
-      S[d4 + 3] = fmaf(a, S[d4 + 3], bv * k4.w); acc3 = fmaf(S[d4 + 3], q4.w, acc3);
+    for (int r = 0; r < DW; r += 4) {
+      float4 k4 = *reinterpret_cast<const float4*>(&sk[warp][r]), q4 = *reinterpret_cast<const float4*>(&sq[warp][r]);
+      S[r] = fmaf(a, S[r], bv * k4.x);         acc0 = fmaf(S[r], q4.x, acc0);
+      S[r + 1] = fmaf(a, S[r + 1], bv * k4.y); acc1 = fmaf(S[r + 1], q4.y, acc1);
+      S[r + 2] = fmaf(a, S[r + 2], bv * k4.z); acc2 = fmaf(S[r + 2], q4.z, acc2);
+      S[r + 3] = fmaf(a, S[r + 3], bv * k4.w); acc3 = fmaf(S[r + 3], q4.w, acc3);
     }
-    if (has_col) out[(size_t)t * n_heads * vdim + (size_t)head * vdim + c] = ((acc0 + acc1) + (acc2 + acc3)) / denom;
+    part_o[buf][warp][lane] = (acc0 + acc1) + (acc2 + acc3);
+    if (lane == 0) part_nq[buf][warp] = nq;
+    __syncthreads();
+    if (warp == 0) {
+      float o = (part_o[buf][0][lane] + part_o[buf][1][lane]) + (part_o[buf][2][lane] + part_o[buf][3][lane]);
+      float nq_all = (part_nq[buf][0] + part_nq[buf][1]) + (part_nq[buf][2] + part_nq[buf][3]);
+      float denom = fmaxf(fabsf(nq_all), expf(-m)) + 1e-6f;
+      if (has_col) out[(size_t)t * n_heads * vdim + (size_t)head * vdim + c] = o / denom;
+    }
   }
   if (has_col) {
 #pragma unroll
-    for (int d = 0; d < D; ++d)
-      if (d < dim) st[(size_t)d * vdim + c] = S[d];
+    for (int r = 0; r < DW; ++r)
+      if (d0 + r < dim) st[(size_t)(d0 + r) * vdim + c] = S[r];
   }
   if (blockIdx.z == 0) {
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-      if (lane + 32 * r < dim) st_n[lane + 32 * r] = n[r];
-    if (lane == 0) st_n[dim] = m;
+    if (has_row) st_n[my_d] = n;
+    if (threadIdx.x == 0) st_n[dim] = m;
   }
 }
 
@@ -220,12 +216,12 @@ static cudaError_t launch_mlstm_warp(const void* qkv, int row_stride, int k_off,
                                      float q_scale, float* out, cudaStream_t stream) {
   dim3 grid(n_seqs, n_heads, (vdim + 31) / 32);
   if (dim <= 32)
-    return bn_launch(mlstm_recurrence_warp_kernel<T, 32>, grid, dim3(32), 0, stream, (const T*)qkv, row_stride, k_off, v_off,
+    return bn_launch(mlstm_recurrence_warp_kernel<T, 32>, grid, dim3(128), 0, stream, (const T*)qkv, row_stride, k_off, v_off,
                      gates, state, seq_start, slots, n_heads, dim, vdim, q_scale, out);
   if (dim <= 64)
-    return bn_launch(mlstm_recurrence_warp_kernel<T, 64>, grid, dim3(32), 0, stream, (const T*)qkv, row_stride, k_off, v_off,
+    return bn_launch(mlstm_recurrence_warp_kernel<T, 64>, grid, dim3(128), 0, stream, (const T*)qkv, row_stride, k_off, v_off,
                      gates, state, seq_start, slots, n_heads, dim, vdim, q_scale, out);
-  return bn_launch(mlstm_recurrence_warp_kernel<T, 128>, grid, dim3(32), 0, stream, (const T*)qkv, row_stride, k_off, v_off,
+  return bn_launch(mlstm_recurrence_warp_kernel<T, 128>, grid, dim3(128), 0, stream, (const T*)qkv, row_stride, k_off, v_off,
                    gates, state, seq_start, slots, n_heads, dim, vdim, q_scale, out);
 }
 

@@ -290,8 +290,10 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
                       tok_pos: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
                       k_cache: torch.Tensor, v_cache: torch.Tensor, *, keep_first: int = 0,
                       rel: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-                      gate_stride: int = 0) -> torch.Tensor:
+                      gate_stride: int = 0, max_keys: int = 0) -> torch.Tensor:
     """Causal attention of every new token over its sequence's pages; q may be a view into a wider row.
+    ``max_keys`` (optional): a bound on the keys any of the tokens sees; with few tokens and many keys the
+    keys of a token are then shared out over several blocks whose results a second kernel merges.
 
     A value head may have another width than a key head (the width of ``v_cache``'s rows).  With a
     window, keys at positions below ``keep_first`` stay visible.  ``rel`` ``[distances, n_heads]``
@@ -325,12 +327,20 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
     if gate is not None:
         if not gate.is_cuda or gate.dtype != q.dtype or gate.stride(-1) != 1 or gate.shape[-1] < n_heads or gate_stride <= 0:
             raise KernelError("attention: gate must be a CUDA view of q's type with unit inner stride and one number per head")
-    if (keep_first or rel is not None or gate is not None or v_dim != head_dim):
+    splits = 1
+    if max_keys > 2 * DECODE_CHUNK and n_tokens * n_heads < 2 * n_sms(q.device):
+        splits = min(16, (max_keys + DECODE_CHUNK - 1) // DECODE_CHUNK, max(1, 4 * n_sms(q.device) // (n_tokens * n_heads)))
+    if (keep_first or rel is not None or gate is not None or v_dim != head_dim or splits > 1):
+        part = None
+        if splits > 1:
+            part = torch.empty(n_tokens * n_heads * splits * (v_dim + 2), dtype=torch.float32, device=q.device)
+            global LAUNCHES
+            LAUNCHES += 1  # the kernel that merges the splits
         _check(_fn("attention", "bn_attention_general_ex")(
             _ptr(q), int(q_stride), _ptr(out), int(out.shape[1]), int(_code(q)), int(n_tokens), int(n_heads),
             int(n_kv_heads), int(head_dim), int(v_dim), c_float(scale), int(window), int(keep_first), _ptr(rel), int(n_rel),
             _ptr(gate), int(gate_stride), _ptr(tok_seq), _ptr(tok_pos), _ptr(slots), _ptr(page_table),
-            int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), _stream()), "attention_general")
+            int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), _ptr(part), int(splits), _stream()), "attention_general")
         return out
     _check(_fn("attention", "bn_attention_general")(
         _ptr(q), int(q_stride), _ptr(out), int(out.shape[1]), int(_code(q)), int(n_tokens), int(n_heads),

@@ -131,6 +131,7 @@ class BiasAttention(Mixer):
         else:
             ops.attention_general(proj, self.row, out, n, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, ctx.tok_seq,
                                   ctx.tok_pos, ctx.slots, kv.page_table, kv.k, kv.v, keep_first=keep,
-                                  rel=self.rel, gate=gate, gate_stride=self.row)
+                                  rel=self.rel, gate=gate, gate_stride=self.row,
+                                  max_keys=min(ctx.max_len, s.window + keep) if s.window > 0 else ctx.max_len)
         ctx.tap("attn_out", out)
         return ops.linear(out, self.w_o, out_dtype=torch.float32)

@@ -28,7 +28,7 @@ TOY = {"architectures": [toy_arch.NAME], "width": 48, "ffn_width": 80, "vocab": 
 
 def test_the_toy_architecture_is_found_by_its_name_and_reads_its_own_keys(tmp_path):
     from bitnet_c_b200.config import ConfigError, architecture_of, known_architectures
-    assert known_architectures() == ["LlamaForCausalLM", toy_arch.NAME]
+    assert {"LlamaForCausalLM", toy_arch.NAME} <= set(known_architectures())
     arch = architecture_of(TOY)
     cfg = arch.read_config(TOY)
     spec = arch.to_spec(cfg)
