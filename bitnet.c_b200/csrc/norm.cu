@@ -188,7 +188,7 @@ extern "C" int bn_add_rmsnorm(float* x, const void* delta, int delta_dtype, int 
 // receives the same values in the compute type for the products that read them next.
 __global__ void scaled_add_rmsnorm_kernel(float* __restrict__ x, float alpha, const void* __restrict__ delta,
                                           int delta_dtype, const void* __restrict__ w, int w_dtype,
-                                          void* __restrict__ out, int out_dtype, int width, float eps) {
+                                          void* __restrict__ out, int out_dtype, int width, float eps, int vec4) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float v[];  // width floats, then 32 for the reduction
@@ -196,18 +196,41 @@ __global__ void scaled_add_rmsnorm_kernel(float* __restrict__ x, float alpha, co
   size_t row = blockIdx.x;
   float* xr = x + row * width;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float a = alpha * xr[i];
-    if (delta) a += load_as_f32(delta, delta_dtype, row * width + i);
-    v[i] = a;
-    ss += a * a;
+  if (vec4) {  // groups of four columns in whole 8- or 16-byte pieces (the launcher checked the alignment)
+    for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+      float4 a = *reinterpret_cast<const float4*>(xr + i);
+      a.x *= alpha; a.y *= alpha; a.z *= alpha; a.w *= alpha;
+      if (delta) {
+        float4 d = load4_as_f32(delta, delta_dtype, row * width + i);
+        a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+      }
+      *reinterpret_cast<float4*>(v + i) = a;
+      ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+    }
+  } else {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+      float a = alpha * xr[i];
+      if (delta) a += load_as_f32(delta, delta_dtype, row * width + i);
+      v[i] = a;
+      ss += a * a;
+    }
   }
   ss = block_sum(ss, scratch);
   float scale = 1.0f / sqrtf(ss / (float)width + eps);
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float y = v[i] * scale * load_as_f32(w, w_dtype, i);
-    xr[i] = y;
-    if (out) store_from_f32(out, out_dtype, row * width + i, y);
+  if (vec4) {
+    for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+      float4 a = *reinterpret_cast<const float4*>(v + i);
+      float4 g = load4_as_f32(w, w_dtype, i);
+      float4 y = make_float4(a.x * scale * g.x, a.y * scale * g.y, a.z * scale * g.z, a.w * scale * g.w);
+      *reinterpret_cast<float4*>(xr + i) = y;
+      if (out) store4_from_f32(out, out_dtype, row * width + i, y);
+    }
+  } else {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+      float y = v[i] * scale * load_as_f32(w, w_dtype, i);
+      xr[i] = y;
+      if (out) store_from_f32(out, out_dtype, row * width + i, y);
+    }
   }
 }
 
@@ -227,8 +250,9 @@ extern "C" int bn_scaled_add_rmsnorm(float* x, float alpha, const void* delta, i
     }
   }
   int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  int vec4 = width % 8 == 0 && (((uintptr_t)x | (uintptr_t)out | (uintptr_t)w | (uintptr_t)delta) & 15) == 0;
   BN_LAUNCH(scaled_add_rmsnorm_kernel, n_rows, threads, smem, stream, x, alpha, delta, delta_dtype, w, w_dtype, out,
-            out_dtype, width, eps);
+            out_dtype, width, eps, vec4);
   BN_CHECK_LAUNCH();
   return BN_OK;
 }
