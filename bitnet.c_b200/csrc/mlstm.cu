@@ -273,6 +273,235 @@ extern "C" int bn_mlstm_recurrence(const void* qkv, int dtype, int row_stride, i
   return BN_OK;
 }
 
+// ---- runs of many tokens: the recurrence chunk by chunk ------------------------------------------
+// Within a chunk of 32 tokens the recurrence is unrolled into sums.  With F_t the sum of the forget
+// gates from the chunk's first token to t, z_s = i_s - F_s and M_t = max(m0, max_{s<=t} z_s)
+// (m0: the stabiliser before the chunk), the stabiliser after token t is m_t = F_t + M_t, and
+//
+//   S_t = sum_{s<=t} e^{z_s - M_t} k_s v_s^T + e^{m0 - M_t} S0        (every exponent is <= 0)
+//
+// so  S_t^T q_t = sum_{s<=t} e^{z_s - M_t} (q_t . k_s) v_s + e^{m0 - M_t} S0^T q_t, likewise n_t . q_t with
+// the v_s left out, and the state after the chunk is S_t, n_t, m_t at its last token.  Per chunk that is
+// four small matrix products in float32 (Q K^T, P V, Q S0, K^T V) instead of 32 dependent steps; the
+// chunks of a sequence follow one another through the state.  One block of 128 threads per (sequence,
+// head, 32 value columns); the 32 tokens of a chunk are the 32 lanes of a warp for the scans.
+// The sums run in another order than token by token, so the two forms agree to rounding, not bit by bit.
+#define MLC_L 32
+#define MLC_THREADS 128
+
+template <typename T>
+__global__ void __launch_bounds__(MLC_THREADS) mlstm_chunk_kernel(
+    const T* __restrict__ qkv, int row_stride, int k_off, int v_off, const float* __restrict__ gates,
+    float* __restrict__ state, const int* __restrict__ seq_start, const int* __restrict__ slots, int n_heads, int dim,
+    int vdim, float q_scale, float* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float sm[];
+  const int ld = dim + 4;                 // padded rows of Q and K
+  float* sQ = sm;                         // [L][ld]
+  float* sK = sQ + MLC_L * ld;            // [L][ld]
+  float* sS = sK + MLC_L * ld;            // [dim][32]
+  float* sV = sS + (size_t)dim * 32;      // [L][32]
+  float* sP = sV + MLC_L * 32;            // [L][L + 1]
+  float* sn = sP + MLC_L * (MLC_L + 1);   // [dim]
+  float* s_nq = sn + dim;                 // [L]
+  float* s_g = s_nq + MLC_L;              // [L]: each token's weight in the state after the chunk
+  const int seq = blockIdx.x, head = blockIdx.y, c0 = blockIdx.z * 32;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int c = c0 + lane;
+  const bool has_col = c < vdim;
+  const size_t per_head = (size_t)dim * vdim + dim + 1;
+  float* st = state + ((size_t)slots[seq] * n_heads + head) * per_head;
+  float* st_n = st + (size_t)dim * vdim;
+  for (int i = tid; i < dim * 32; i += MLC_THREADS) {
+    int d = i >> 5, cc = i & 31;
+    sS[i] = (c0 + cc < vdim) ? st[(size_t)d * vdim + c0 + cc] : 0.f;
+  }
+  for (int d = tid; d < dim; d += MLC_THREADS) sn[d] = st_n[d];
+  float m0 = st_n[dim];
+  const int t0 = seq_start[seq], t1 = seq_start[seq + 1];
+  for (int base = t0; base < t1; base += MLC_L) {
+    const int n_tok = min(MLC_L, t1 - base);
+    __syncthreads();  // the chunk before is done with sQ, sK, sV, sP; sS and sn are up to date
+    for (int i = tid; i < MLC_L * dim; i += MLC_THREADS) {
+      int t = i / dim, d = i - t * dim;
+      bool ok = t < n_tok;
+      const T* row = qkv + (size_t)(base + t) * row_stride;
+      sQ[t * ld + d] = ok ? to_f32<T>(row[(size_t)head * dim + d]) * q_scale : 0.f;
+      sK[t * ld + d] = ok ? to_f32<T>(row[k_off + (size_t)head * dim + d]) : 0.f;
+    }
+    for (int i = tid; i < MLC_L * 32; i += MLC_THREADS) {
+      int t = i >> 5, cc = i & 31;
+      sV[i] = (t < n_tok && c0 + cc < vdim) ? to_f32<T>(qkv[(size_t)(base + t) * row_stride + v_off + (size_t)head * vdim + c0 + cc]) : 0.f;
+    }
+    // the chunk's scalars, in every warp alike: lane = token
+    const bool valid = lane < n_tok;
+    float gi = valid ? gates[(size_t)(base + lane) * 2 * n_heads + head] : 0.f;
+    float gf = valid ? gates[(size_t)(base + lane) * 2 * n_heads + n_heads + head] : 0.f;
+    float F = gf;  // inclusive sum over the lanes
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      float up = __shfl_up_sync(0xffffffffu, F, o);
+      if (lane >= o) F += up;
+    }
+    float z = valid ? gi - F : -INFINITY;
+    float G = z;   // inclusive maximum over the lanes
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      float up = __shfl_up_sync(0xffffffffu, G, o);
+      if (lane >= o) G = fmaxf(G, up);
+    }
+    const float M = fmaxf(m0, G);          // M_t of this lane's token
+    const float carry = expf(m0 - M);      // weight of the state before the chunk at this token
+    const float m_tok = F + M;             // the stabiliser after this token
+    const float M_last = __shfl_sync(0xffffffffu, M, n_tok - 1);
+    const float g_state = valid ? expf(z - M_last) : 0.f;  // weight of this token in the state after the chunk
+    const float carry_last = expf(m0 - M_last);
+    const float m_end = __shfl_sync(0xffffffffu, m_tok, n_tok - 1);
+    if (warp == 0) s_g[lane] = g_state;
+    __syncthreads();  // sQ, sK, sV, s_g are loaded
+    // ---- P[t][s] = (q_t . k_s) e^{z_s - M_t} for s <= t: thread = (row t, eight columns s)
+    {
+      const int t = tid >> 2, s0 = (tid & 3) * 8;
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      if (s0 <= t) {
+        for (int d = 0; d < dim; d += 4) {
+          float4 q4 = *reinterpret_cast<const float4*>(sQ + t * ld + d);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 k4 = *reinterpret_cast<const float4*>(sK + (s0 + j) * ld + d);
+            acc[j] = fmaf(q4.x, k4.x, acc[j]); acc[j] = fmaf(q4.y, k4.y, acc[j]);
+            acc[j] = fmaf(q4.z, k4.z, acc[j]); acc[j] = fmaf(q4.w, k4.w, acc[j]);
+          }
+        }
+      }
+      const float M_t = __shfl_sync(0xffffffffu, M, t);  // lanes of one warp hold rows warp * 8 .. + 8: t is a lane's token
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        int sidx = s0 + j;
+        float z_s = __shfl_sync(0xffffffffu, z, sidx);
+        sP[t * (MLC_L + 1) + sidx] = (sidx <= t && sidx < n_tok) ? acc[j] * expf(z_s - M_t) : 0.f;
+      }
+    }
+    __syncthreads();
+    // ---- n_t . q_t = sum_s P[t][s] + carry_t (q_t . n0): warp w takes rows w * 8 .. + 8, lanes share the sums
+    for (int r = 0; r < 8; ++r) {
+      const int t = warp * 8 + r;
+      float part = sP[t * (MLC_L + 1) + lane];
+      float qn = 0.f;
+      for (int d = lane; d < dim; d += 32) qn = fmaf(sQ[t * ld + d], sn[d], qn);
+      part = warp_sum(part);
+      qn = warp_sum(qn);
+      if (lane == 0) s_nq[t] = part;  // completed below with the row's carry times q_t . n0
+      if (lane == 1) sP[t * (MLC_L + 1) + MLC_L] = qn;  // the spare column keeps q_t . n0
+    }
+    __syncthreads();
+    // ---- numerators: thread = (column, eight rows); then the outputs
+    {
+      const int r0 = warp * 8;
+      float acc[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) acc[r] = 0.f;
+      for (int d = 0; d < dim; d += 4) {
+        float s0v = sS[d * 32 + lane], s1v = sS[(d + 1) * 32 + lane], s2v = sS[(d + 2) * 32 + lane], s3v = sS[(d + 3) * 32 + lane];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          float4 q4 = *reinterpret_cast<const float4*>(sQ + (r0 + r) * ld + d);
+          acc[r] = fmaf(q4.x, s0v, acc[r]); acc[r] = fmaf(q4.y, s1v, acc[r]);
+          acc[r] = fmaf(q4.z, s2v, acc[r]); acc[r] = fmaf(q4.w, s3v, acc[r]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 8; ++r) acc[r] *= __shfl_sync(0xffffffffu, carry, r0 + r);
+      for (int sidx = 0; sidx < n_tok; ++sidx) {
+        float v = sV[sidx * 32 + lane];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) acc[r] = fmaf(sP[(r0 + r) * (MLC_L + 1) + sidx], v, acc[r]);
+      }
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const int t = r0 + r;
+        float nq = s_nq[t] + __shfl_sync(0xffffffffu, carry, t) * sP[t * (MLC_L + 1) + MLC_L];
+        float denom = fmaxf(fabsf(nq), expf(-__shfl_sync(0xffffffffu, m_tok, t))) + 1e-6f;
+        if (t < n_tok && has_col) out[(size_t)(base + t) * n_heads * vdim + (size_t)head * vdim + c] = acc[r] / denom;
+      }
+    }
+    __syncthreads();  // everyone has read sS and sn as they were before the chunk
+    // ---- the state after the chunk: thread = (column, sixteen rows d at a time; the warps take turns)
+    for (int dbase = warp * 16; dbase < dim; dbase += 64) {
+      float acc[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+      for (int sidx = 0; sidx < n_tok; ++sidx) {
+        const float gv = s_g[sidx] * sV[sidx * 32 + lane];
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) {
+          // rows are padded by four and followed by other arrays: a read past dim stays inside and is not kept
+          float4 k4 = *reinterpret_cast<const float4*>(sK + sidx * ld + dbase + j);
+          acc[j] = fmaf(gv, k4.x, acc[j]);         acc[j + 1] = fmaf(gv, k4.y, acc[j + 1]);
+          acc[j + 2] = fmaf(gv, k4.z, acc[j + 2]); acc[j + 3] = fmaf(gv, k4.w, acc[j + 3]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (dbase + j < dim) sS[(dbase + j) * 32 + lane] = fmaf(carry_last, sS[(dbase + j) * 32 + lane], acc[j]);
+    }
+    for (int d = tid; d < dim; d += MLC_THREADS) {
+      float acc = 0.f;
+      for (int sidx = 0; sidx < n_tok; ++sidx) acc = fmaf(s_g[sidx], sK[sidx * ld + d], acc);
+      sn[d] = fmaf(carry_last, sn[d], acc);
+    }
+    m0 = m_end;
+  }
+  __syncthreads();
+  for (int i = tid; i < dim * 32; i += MLC_THREADS) {
+    int d = i >> 5, cc = i & 31;
+    if (c0 + cc < vdim) st[(size_t)d * vdim + c0 + cc] = sS[i];
+  }
+  if (blockIdx.z == 0) {
+    for (int d = tid; d < dim; d += MLC_THREADS) st_n[d] = sn[d];
+    if (tid == 0) st_n[dim] = m0;
+  }
+}
+
+// As bn_mlstm_recurrence, by chunks of 32 tokens (for steps that bring runs of many tokens).
+extern "C" int bn_mlstm_chunks(const void* qkv, int dtype, int row_stride, int k_off, int v_off, const float* gates,
+                               float* state, const int* seq_start, const int* slots, int n_seqs, int n_heads, int dim,
+                               int vdim, float q_scale, float* out, cudaStream_t stream) {
+  if (n_seqs <= 0) return BN_OK;
+  if (!qkv || !gates || !state || !out || n_heads <= 0 || dim <= 0 || dim % 4 || vdim <= 0 || n_heads > 65535 ||
+      (vdim + 31) / 32 > 65535)
+    return BN_ERR_BAD_ARG;
+  size_t floats = 2 * (size_t)MLC_L * (dim + 4) + (size_t)dim * 32 + MLC_L * 32 + MLC_L * (MLC_L + 1) + dim + 2 * MLC_L;
+  size_t smem = floats * sizeof(float);
+  if (smem > 200 * 1024) return BN_ERR_BAD_ARG;
+  dim3 grid(n_seqs, n_heads, (vdim + 31) / 32);
+  static size_t granted_f = 0, granted_b = 0;
+  if (dtype == BN_F32) {
+    if (smem > 48 * 1024 && smem > granted_f) {
+      cudaError_t e = cudaFuncSetAttribute(mlstm_chunk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
+      granted_f = smem;
+    }
+    BN_LAUNCH(mlstm_chunk_kernel<float>, grid, MLC_THREADS, smem, stream, (const float*)qkv, row_stride, k_off, v_off, gates,
+              state, seq_start, slots, n_heads, dim, vdim, q_scale, out);
+  } else if (dtype == BN_BF16) {
+    if (smem > 48 * 1024 && smem > granted_b) {
+      cudaError_t e = cudaFuncSetAttribute(mlstm_chunk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
+      granted_b = smem;
+    }
+    BN_LAUNCH(mlstm_chunk_kernel<__nv_bfloat16>, grid, MLC_THREADS, smem, stream, (const __nv_bfloat16*)qkv, row_stride, k_off,
+              v_off, gates, state, seq_start, slots, n_heads, dim, vdim, q_scale, out);
+  } else {
+    return BN_ERR_BAD_ARG;
+  }
+  BN_CHECK_LAUNCH();
+  return BN_OK;
+}
+
 // out[t][h][c] = o[t][h][c] / sqrt(mean_c(o[t][h]^2) + eps) * gain[h * vdim + c] * sigmoid(g[t][h * vdim + c])
 template <typename T, typename W>
 __global__ void mlstm_output_kernel(const float* __restrict__ o, const W* __restrict__ gain, const T* __restrict__ g,

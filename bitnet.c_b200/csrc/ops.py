@@ -1025,11 +1025,12 @@ def mlstm_state_floats(dim: int, vdim: int) -> int:
 
 def mlstm_recurrence(qkv: torch.Tensor, k_off: int, v_off: int, gates: torch.Tensor, state: torch.Tensor,
                      seq_start: torch.Tensor, slots: torch.Tensor, n_seqs: int, n_heads: int, dim: int, vdim: int,
-                     q_scale: float) -> torch.Tensor:
+                     q_scale: float, chunks: bool = False) -> torch.Tensor:
     """The matrix-memory recurrence over the new tokens of every sequence, from and into ``state``
     ``[slots, heads, mlstm_state_floats]`` (float32); returns the heads' raw outputs, float32
     ``[T, heads * vdim]``.  Rows of ``qkv`` hold the query heads first, key heads at ``k_off``, value heads
-    at ``v_off``."""
+    at ``v_off``.  ``chunks``: for runs of many tokens, the same sums taken 32 tokens at a time as small matrix
+    products (head sizes in multiples of 4; agrees with the token-by-token form to rounding)."""
     _need(qkv, "qkv", dims=2)
     _need(gates, "gates", torch.float32, 2)
     _need(state, "state", torch.float32, 3)
@@ -1041,7 +1042,8 @@ def mlstm_recurrence(qkv: torch.Tensor, k_off: int, v_off: int, gates: torch.Ten
             or seq_start.shape[0] < n_seqs + 1 or slots.shape[0] < n_seqs):
         raise KernelError("mlstm_recurrence: sizes do not fit")
     out = torch.empty((T, n_heads * vdim), dtype=torch.float32, device=qkv.device)
-    _check(_fn("mlstm", "bn_mlstm_recurrence")(_ptr(qkv), int(_code(qkv)), int(qkv.shape[1]), int(k_off), int(v_off),
+    entry = "bn_mlstm_chunks" if chunks and dim % 4 == 0 and (2 * 32 * (dim + 4) + 33 * dim + 2200) * 4 <= 200 * 1024 else "bn_mlstm_recurrence"
+    _check(_fn("mlstm", entry)(_ptr(qkv), int(_code(qkv)), int(qkv.shape[1]), int(k_off), int(v_off),
                                                _ptr(gates), _ptr(state), _ptr(seq_start), _ptr(slots), int(n_seqs),
                                                int(n_heads), int(dim), int(vdim), c_float(q_scale), _ptr(out), _stream()),
            "mlstm_recurrence")

@@ -24,6 +24,7 @@ class Mlstm(Mixer):
 
     kernels = ("linear", "linear_mma", "linear_tc", "gemm_tc", "mlstm")
     graph_safe = True
+    CHUNKED_MIN_TOKENS = 16  # bfloat16 steps with a run of so many new tokens take the recurrence chunk by chunk
 
     def __init__(self, spec, build):
         super().__init__(spec, build)
@@ -66,7 +67,9 @@ class Mlstm(Mixer):
         proj = ops.linear(h, self.w_in, out_dtype=self.build.dtype)
         gates = ops.mlstm_gates(h, self.w_gates, self.b_gates, s.n_heads, s.gate_cap)
         o = ops.mlstm_recurrence(proj, self.k_off, self.v_off, gates, state, ctx.seq_start, ctx.slots, ctx.n_seqs,
-                                 s.n_heads, s.head_dim, s.v_head_dim, s.head_dim ** -0.5)
+                                 s.n_heads, s.head_dim, s.v_head_dim, s.head_dim ** -0.5,
+                                 chunks=(self.build.dtype == torch.bfloat16 and not ctx.decode
+                                         and ctx.max_new >= self.CHUNKED_MIN_TOKENS))
         ctx.tap("mlstm_raw", o)
         y = ops.mlstm_output(o, self.gain, proj[:, self.g_off: self.g_off + s.n_heads * s.v_head_dim], self.row,
                              s.n_heads, s.v_head_dim, s.norm_eps, self.build.dtype)

@@ -79,6 +79,25 @@ CASE_C = {
 REL_ROWS_C = {0: 32, 1: 20, 2: 24}
 
 
+# sizes that are no multiples of 8 anywhere: rows of no whole 16-byte pieces, so every kernel takes its
+# number-by-number path and the products the library's
+CASE_D = {
+    "architecture": "Fesorax", "vocab": 61, "width": 50, "postln_alpha": 2.0, "norm": {"eps": 1e-5},
+    "embedding": {"scale": 5.0},
+    "layers": [
+        {"type": "attention", "mixer": {"heads": 3, "kv_heads": 1, "dim": 20, "vdim": 12, "scale": 0.7, "bias_max": 25,
+                                        "mask": {"size": 30, "keep_first": 2}},
+         "mlp": {"kind": "moe", "router": {"experts": 3, "top": 2}, "expert": {"ff": 18, "limit": 1.0},
+                 "shared": {"ff": 10, "limit": 1.0}}},
+        {"type": "mlstm", "mixer": {"heads": 2, "dim": 20, "vdim": 36, "gate_cap": 8.0}, "mlp": None},
+        {"type": "attention", "mixer": {"heads": 3, "kv_heads": 1, "dim": 20, "vdim": 12, "scale": 0.7, "bias_max": 25,
+                                        "kv_from": 0},
+         "mlp": {"kind": "moe", "router": {"experts": 2, "top": 1}, "expert": {"ff": 6, "limit": 2.0}}},
+    ],
+}
+REL_ROWS_D = {0: 10, 2: 14}
+
+
 def tensor_shapes(cfg: dict, rel_rows: dict) -> dict:
     """Every tensor of the design by name, from the configuration alone."""
     W = cfg["width"]

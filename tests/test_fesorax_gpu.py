@@ -83,6 +83,20 @@ def test_mlstm_kernels_alone_and_carrying_their_state(cuda_device, H, d, dv, dty
     got[step2] = o.cpu().numpy()
     assert np.abs(got - want).max() < 2e-4 * max(1.0, np.abs(want).max())
     assert bool((state[1] == 7.0).all()) and bool((state[2] == 0.0).all())
+    # the same by chunks of 32 tokens (other order of the sums), in the same two steps, and the states agree
+    state2 = torch.zeros_like(state)
+    got2 = np.zeros_like(got)
+    for rows_of, starts_of, slots_of in ((step1, first, slots[:2]), (step2, [0, 17, 29], slots[[0, 2]])):
+        o = ops.mlstm_recurrence(rows[rows_of].contiguous(), H * d, 2 * H * d, gates[rows_of].contiguous(), state2,
+                                 torch.tensor(starts_of, dtype=torch.int32, device="cuda"), slots_of.contiguous(), 2, H, d, dv,
+                                 d ** -0.5, chunks=True)
+        got2[rows_of] = o.cpu().numpy()
+    assert np.abs(got2 - want).max() < 5e-4 * max(1.0, np.abs(want).max())
+    live = [0, 3, 4]
+    # S and n are kept relative to the stabiliser m: compare what they stand for, e^m S
+    a, b = state[live].cpu().numpy().astype(np.float64), state2[live].cpu().numpy().astype(np.float64)
+    assert np.abs(a[..., -1] - b[..., -1]).max() < 1e-3
+    assert np.abs(a[..., :-1] - b[..., :-1] * np.exp(b[..., -1:] - a[..., -1:])).max() < 1e-3 * max(1.0, np.abs(a[..., :-1]).max())
     gain, g = bf(1 + 0.3 * rng.standard_normal(H * dv)), bf(rng.standard_normal((T, H * dv)))
     y = ops.mlstm_output(dev(want), dev(gain, t), dev(g, t), H * dv, H, dv, 1e-5, t).float().cpu().numpy()
     ref = (pf.unit_rms(want.astype(np.float32).reshape(T, H, dv).astype(np.float64), 1e-5).reshape(T, H * dv) * gain * pf.sigmoid(g))
@@ -132,7 +146,8 @@ def test_mixture_of_experts_few_rows_and_many_rows(cuda_device, E, top, ff, shar
 
 
 # ---- whole models ------------------------------------------------------------------------------------
-CASES = {"A": (fc.CASE_A, fc.REL_ROWS_A), "B": (fc.CASE_B, fc.REL_ROWS_B), "C": (fc.CASE_C, fc.REL_ROWS_C)}
+CASES = {"A": (fc.CASE_A, fc.REL_ROWS_A), "B": (fc.CASE_B, fc.REL_ROWS_B), "C": (fc.CASE_C, fc.REL_ROWS_C),
+         "D": (fc.CASE_D, fc.REL_ROWS_D)}
 
 
 @pytest.fixture(scope="module")
@@ -181,7 +196,7 @@ def _poison(cache):
         g.v.fill_(float("inf"))
 
 
-@pytest.mark.parametrize("case", ["A", "B", "C"])
+@pytest.mark.parametrize("case", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_models_step_like_the_plain_statement_however_the_tokens_are_cut(folders, cuda_device, case, dtype):
     cfg = CASES[case][0]
