@@ -320,19 +320,71 @@ __global__ void __launch_bounds__(MLC_THREADS) mlstm_chunk_kernel(
   for (int d = tid; d < dim; d += MLC_THREADS) sn[d] = st_n[d];
   float m0 = st_n[dim];
   const int t0 = seq_start[seq], t1 = seq_start[seq + 1];
+  // Rows of whole 16-byte pieces (the usual case) are read in such pieces, and a chunk's q and k rows are
+  // requested into registers while the chunk before is worked on; other sizes go number by number.
+  constexpr int VN = 16 / sizeof(T);
+  constexpr int MAXV = 8;  // pieces per thread and matrix: 32 rows of up to 256 numbers in float32, 512 in bfloat16
+  const bool wide = dim % VN == 0 && k_off % VN == 0 && row_stride % VN == 0 && v_off % VN == 0 && vdim % VN == 0 &&
+                    (((uintptr_t)qkv) & 15) == 0 && MLC_L * dim / VN <= MAXV * MLC_THREADS;
+  const int pieces = wide ? MLC_L * dim / VN : 0, per_row = wide ? dim / VN : 1;
+  uint4 rq[MAXV], rk[MAXV];
+  auto request = [&](int base) {
+    const int n_tok = min(MLC_L, t1 - base);
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+      int idx = tid + j * MLC_THREADS;
+      int t = idx / per_row, d = (idx - t * per_row) * VN;
+      if (idx < pieces && t < n_tok) {
+        const T* row = qkv + (size_t)(base + t) * row_stride + (size_t)head * dim + d;
+        rq[j] = *reinterpret_cast<const uint4*>(row);
+        rk[j] = *reinterpret_cast<const uint4*>(row + k_off);
+      } else {
+        rq[j] = make_uint4(0, 0, 0, 0);
+        rk[j] = make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  auto unpack = [&](const uint4& raw, float* dst, float scale) {
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < VN; ++i) dst[i] = to_f32<T>(e[i]) * scale;
+  };
+  if (wide && t0 < t1) request(t0);
   for (int base = t0; base < t1; base += MLC_L) {
     const int n_tok = min(MLC_L, t1 - base);
     __syncthreads();  // the chunk before is done with sQ, sK, sV, sP; sS and sn are up to date
-    for (int i = tid; i < MLC_L * dim; i += MLC_THREADS) {
-      int t = i / dim, d = i - t * dim;
-      bool ok = t < n_tok;
-      const T* row = qkv + (size_t)(base + t) * row_stride;
-      sQ[t * ld + d] = ok ? to_f32<T>(row[(size_t)head * dim + d]) * q_scale : 0.f;
-      sK[t * ld + d] = ok ? to_f32<T>(row[k_off + (size_t)head * dim + d]) : 0.f;
+    if (wide) {
+#pragma unroll
+      for (int j = 0; j < MAXV; ++j) {
+        int idx = tid + j * MLC_THREADS;
+        if (idx < pieces) {
+          int t = idx / per_row, d = (idx - t * per_row) * VN;
+          unpack(rq[j], sQ + t * ld + d, q_scale);
+          unpack(rk[j], sK + t * ld + d, 1.0f);
+        }
+      }
+      if (base + MLC_L < t1) request(base + MLC_L);
+    } else {
+      for (int i = tid; i < MLC_L * dim; i += MLC_THREADS) {
+        int t = i / dim, d = i - t * dim;
+        bool ok = t < n_tok;
+        const T* row = qkv + (size_t)(base + t) * row_stride;
+        sQ[t * ld + d] = ok ? to_f32<T>(row[(size_t)head * dim + d]) * q_scale : 0.f;
+        sK[t * ld + d] = ok ? to_f32<T>(row[k_off + (size_t)head * dim + d]) : 0.f;
+      }
     }
-    for (int i = tid; i < MLC_L * 32; i += MLC_THREADS) {
-      int t = i >> 5, cc = i & 31;
-      sV[i] = (t < n_tok && c0 + cc < vdim) ? to_f32<T>(qkv[(size_t)(base + t) * row_stride + v_off + (size_t)head * vdim + c0 + cc]) : 0.f;
+    if (wide && c0 + 32 <= vdim) {
+      for (int idx = tid; idx < MLC_L * 32 / VN; idx += MLC_THREADS) {
+        int t = idx / (32 / VN), cc = (idx - t * (32 / VN)) * VN;
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (t < n_tok) raw = *reinterpret_cast<const uint4*>(qkv + (size_t)(base + t) * row_stride + v_off + (size_t)head * vdim + c0 + cc);
+        unpack(raw, sV + t * 32 + cc, 1.0f);
+      }
+    } else {
+      for (int i = tid; i < MLC_L * 32; i += MLC_THREADS) {
+        int t = i >> 5, cc = i & 31;
+        sV[i] = (t < n_tok && c0 + cc < vdim) ? to_f32<T>(qkv[(size_t)(base + t) * row_stride + v_off + (size_t)head * vdim + c0 + cc]) : 0.f;
+      }
     }
     // the chunk's scalars, in every warp alike: lane = token
     const bool valid = lane < n_tok;
