@@ -287,7 +287,8 @@ extern "C" int bn_mlstm_recurrence(const void* qkv, int dtype, int row_stride, i
 // head, 32 value columns); the 32 tokens of a chunk are the 32 lanes of a warp for the scans.
 // The sums run in another order than token by token, so the two forms agree to rounding, not bit by bit.
 #define MLC_L 32
-#define MLC_THREADS 128
+#define MLC_THREADS 256
+#define MLC_ROWS (MLC_L / (MLC_THREADS / 32))  // rows of a chunk per warp
 
 template <typename T>
 __global__ void __launch_bounds__(MLC_THREADS) mlstm_chunk_kernel(
@@ -323,7 +324,7 @@ __global__ void __launch_bounds__(MLC_THREADS) mlstm_chunk_kernel(
   // Rows of whole 16-byte pieces (the usual case) are read in such pieces, and a chunk's q and k rows are
   // requested into registers while the chunk before is worked on; other sizes go number by number.
   constexpr int VN = 16 / sizeof(T);
-  constexpr int MAXV = 8;  // pieces per thread and matrix: 32 rows of up to 256 numbers in float32, 512 in bfloat16
+  constexpr int MAXV = 4;  // pieces per thread and matrix: 32 rows of up to 128 numbers in float32, 256 in bfloat16
   const bool wide = dim % VN == 0 && k_off % VN == 0 && row_stride % VN == 0 && v_off % VN == 0 && vdim % VN == 0 &&
                     (((uintptr_t)qkv) & 15) == 0 && MLC_L * dim / VN <= MAXV * MLC_THREADS;
   const int pieces = wide ? MLC_L * dim / VN : 0, per_row = wide ? dim / VN : 1;
@@ -412,35 +413,35 @@ __global__ void __launch_bounds__(MLC_THREADS) mlstm_chunk_kernel(
     const float m_end = __shfl_sync(0xffffffffu, m_tok, n_tok - 1);
     if (warp == 0) s_g[lane] = g_state;
     __syncthreads();  // sQ, sK, sV, s_g are loaded
-    // ---- P[t][s] = (q_t . k_s) e^{z_s - M_t} for s <= t: thread = (row t, eight columns s)
+    // ---- P[t][s] = (q_t . k_s) e^{z_s - M_t} for s <= t: thread = (row t, four columns s)
     {
-      const int t = tid >> 2, s0 = (tid & 3) * 8;
-      float acc[8];
+      const int t = tid >> 3, s0 = (tid & 7) * 4;
+      float acc[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int j = 0; j < 4; ++j) acc[j] = 0.f;
       if (s0 <= t) {
         for (int d = 0; d < dim; d += 4) {
           float4 q4 = *reinterpret_cast<const float4*>(sQ + t * ld + d);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
+          for (int j = 0; j < 4; ++j) {
             float4 k4 = *reinterpret_cast<const float4*>(sK + (s0 + j) * ld + d);
             acc[j] = fmaf(q4.x, k4.x, acc[j]); acc[j] = fmaf(q4.y, k4.y, acc[j]);
             acc[j] = fmaf(q4.z, k4.z, acc[j]); acc[j] = fmaf(q4.w, k4.w, acc[j]);
           }
         }
       }
-      const float M_t = __shfl_sync(0xffffffffu, M, t);  // lanes of one warp hold rows warp * 8 .. + 8: t is a lane's token
+      const float M_t = __shfl_sync(0xffffffffu, M, t);  // every warp holds all tokens' scalars, lane = token
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 4; ++j) {
         int sidx = s0 + j;
         float z_s = __shfl_sync(0xffffffffu, z, sidx);
         sP[t * (MLC_L + 1) + sidx] = (sidx <= t && sidx < n_tok) ? acc[j] * expf(z_s - M_t) : 0.f;
       }
     }
     __syncthreads();
-    // ---- n_t . q_t = sum_s P[t][s] + carry_t (q_t . n0): warp w takes rows w * 8 .. + 8, lanes share the sums
-    for (int r = 0; r < 8; ++r) {
-      const int t = warp * 8 + r;
+    // ---- n_t . q_t = sum_s P[t][s] + carry_t (q_t . n0): a warp takes MLC_ROWS rows, lanes share the sums
+    for (int r = 0; r < MLC_ROWS; ++r) {
+      const int t = warp * MLC_ROWS + r;
       float part = sP[t * (MLC_L + 1) + lane];
       float qn = 0.f;
       for (int d = lane; d < dim; d += 32) qn = fmaf(sQ[t * ld + d], sn[d], qn);
@@ -450,30 +451,30 @@ __global__ void __launch_bounds__(MLC_THREADS) mlstm_chunk_kernel(
       if (lane == 1) sP[t * (MLC_L + 1) + MLC_L] = qn;  // the spare column keeps q_t . n0
     }
     __syncthreads();
-    // ---- numerators: thread = (column, eight rows); then the outputs
+    // ---- numerators: thread = (column, MLC_ROWS rows); then the outputs
     {
-      const int r0 = warp * 8;
-      float acc[8];
+      const int r0 = warp * MLC_ROWS;
+      float acc[MLC_ROWS];
 #pragma unroll
-      for (int r = 0; r < 8; ++r) acc[r] = 0.f;
+      for (int r = 0; r < MLC_ROWS; ++r) acc[r] = 0.f;
       for (int d = 0; d < dim; d += 4) {
         float s0v = sS[d * 32 + lane], s1v = sS[(d + 1) * 32 + lane], s2v = sS[(d + 2) * 32 + lane], s3v = sS[(d + 3) * 32 + lane];
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
+        for (int r = 0; r < MLC_ROWS; ++r) {
           float4 q4 = *reinterpret_cast<const float4*>(sQ + (r0 + r) * ld + d);
           acc[r] = fmaf(q4.x, s0v, acc[r]); acc[r] = fmaf(q4.y, s1v, acc[r]);
           acc[r] = fmaf(q4.z, s2v, acc[r]); acc[r] = fmaf(q4.w, s3v, acc[r]);
         }
       }
 #pragma unroll
-      for (int r = 0; r < 8; ++r) acc[r] *= __shfl_sync(0xffffffffu, carry, r0 + r);
+      for (int r = 0; r < MLC_ROWS; ++r) acc[r] *= __shfl_sync(0xffffffffu, carry, r0 + r);
       for (int sidx = 0; sidx < n_tok; ++sidx) {
         float v = sV[sidx * 32 + lane];
 #pragma unroll
-        for (int r = 0; r < 8; ++r) acc[r] = fmaf(sP[(r0 + r) * (MLC_L + 1) + sidx], v, acc[r]);
+        for (int r = 0; r < MLC_ROWS; ++r) acc[r] = fmaf(sP[(r0 + r) * (MLC_L + 1) + sidx], v, acc[r]);
       }
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
+      for (int r = 0; r < MLC_ROWS; ++r) {
         const int t = r0 + r;
         float nq = s_nq[t] + __shfl_sync(0xffffffffu, carry, t) * sP[t * (MLC_L + 1) + MLC_L];
         float denom = fmaxf(fabsf(nq), expf(-__shfl_sync(0xffffffffu, m_tok, t))) + 1e-6f;
@@ -482,7 +483,7 @@ __global__ void __launch_bounds__(MLC_THREADS) mlstm_chunk_kernel(
     }
     __syncthreads();  // everyone has read sS and sn as they were before the chunk
     // ---- the state after the chunk: thread = (column, sixteen rows d at a time; the warps take turns)
-    for (int dbase = warp * 16; dbase < dim; dbase += 64) {
+    for (int dbase = warp * 16; dbase < dim; dbase += 16 * (MLC_THREADS / 32)) {
       float acc[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) acc[j] = 0.f;
