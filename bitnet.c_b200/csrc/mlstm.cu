@@ -345,10 +345,12 @@ __global__ void __launch_bounds__(MLC_THREADS) mlstm_chunk_kernel(
       }
     }
   };
-  auto unpack = [&](const uint4& raw, float* dst, float scale) {
+  auto unpack = [&](const uint4& raw, float* dst, float scale) {  // dst is 16-byte aligned
     const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-    for (int i = 0; i < VN; ++i) dst[i] = to_f32<T>(e[i]) * scale;
+    for (int i = 0; i < VN; i += 4)
+      *reinterpret_cast<float4*>(dst + i) = make_float4(to_f32<T>(e[i]) * scale, to_f32<T>(e[i + 1]) * scale,
+                                                        to_f32<T>(e[i + 2]) * scale, to_f32<T>(e[i + 3]) * scale);
   };
   if (wide && t0 < t1) request(t0);
   for (int base = t0; base < t1; base += MLC_L) {
@@ -413,18 +415,20 @@ __global__ void __launch_bounds__(MLC_THREADS) mlstm_chunk_kernel(
     const float m_end = __shfl_sync(0xffffffffu, m_tok, n_tok - 1);
     if (warp == 0) s_g[lane] = g_state;
     __syncthreads();  // sQ, sK, sV, s_g are loaded
-    // ---- P[t][s] = (q_t . k_s) e^{z_s - M_t} for s <= t: thread = (row t, four columns s)
+    // ---- P[t][s] = (q_t . k_s) e^{z_s - M_t} for s <= t: thread = (row t, columns s = (tid & 7) + 8 j), so that
+    // the eight threads of a row read eight neighbouring rows of K (rows lie dim + 4 numbers apart: no two in one bank)
     {
-      const int t = tid >> 3, s0 = (tid & 7) * 4;
+      const int t = tid >> 3, s0 = tid & 7;
       float acc[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[j] = 0.f;
-      if (s0 <= t) {
-        for (int d = 0; d < dim; d += 4) {
-          float4 q4 = *reinterpret_cast<const float4*>(sQ + t * ld + d);
+      const int n_col = (t - s0 + 8) >> 3;  // how many of this thread's columns lie at or below the diagonal
+      for (int d = 0; d < dim; d += 4) {
+        float4 q4 = *reinterpret_cast<const float4*>(sQ + t * ld + d);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float4 k4 = *reinterpret_cast<const float4*>(sK + (s0 + j) * ld + d);
+        for (int j = 0; j < 4; ++j) {
+          if (j < n_col) {
+            float4 k4 = *reinterpret_cast<const float4*>(sK + (s0 + 8 * j) * ld + d);
             acc[j] = fmaf(q4.x, k4.x, acc[j]); acc[j] = fmaf(q4.y, k4.y, acc[j]);
             acc[j] = fmaf(q4.z, k4.z, acc[j]); acc[j] = fmaf(q4.w, k4.w, acc[j]);
           }
@@ -433,7 +437,7 @@ __global__ void __launch_bounds__(MLC_THREADS) mlstm_chunk_kernel(
       const float M_t = __shfl_sync(0xffffffffu, M, t);  // every warp holds all tokens' scalars, lane = token
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        int sidx = s0 + j;
+        int sidx = s0 + 8 * j;
         float z_s = __shfl_sync(0xffffffffu, z, sidx);
         sP[t * (MLC_L + 1) + sidx] = (sidx <= t && sidx < n_tok) ? acc[j] * expf(z_s - M_t) : 0.f;
       }
