@@ -273,3 +273,31 @@ def test_greedy_generation_through_the_entry_point_and_the_replay_program(folder
     plain = {k: pf.forward(cfg, w, t) for k, t in reqs.items()}
     compare(collect_trace_output(steps, out, V), plain, lambda ref: TOL_F32 * max(1.0, float(np.abs(ref).max())),
             "through bin/trace_run")
+
+
+def test_the_command_line_writes_a_random_model_of_the_design_and_generates_from_it(tmp_path, cuda_device):
+    import json
+    cfgp = tmp_path / "cfg.json"
+    cfgp.write_text(json.dumps(fc.CASE_C))
+    folder = tmp_path / "m"
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "bitnet"), str(folder), "--random-weights", "--config", str(cfgp),
+           "--weight-seed", "3", "--dtype", "float32", "--prompt-token-ids", "5,17,3,9,9,1", "--prompt-token-ids", "7",
+           "-n", "9", "--repeat-penalty", "1.0", "--token-ids"]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [[int(t) for t in l.split(",")] for l in p.stdout.splitlines() if l.strip()]
+    assert [len(l) for l in lines] == [9, 9] and "Generation complete tokens=18" in p.stderr
+    # the folder it wrote: the design's tensor names (the bias tables with the default number of rows), and the
+    # tokens are the plain statement's greedy choice
+    cfg, w = plain_llama.read_model(str(folder))
+    assert w["l0.mix.rel"].shape == (32, 4) and "l1.mix.k" not in w and "l2.mlp.e2.down" in w
+    for prompt, toks in zip(([5, 17, 3, 9, 9, 1], [7]), lines):
+        ref = pf.forward(cfg, w, prompt + toks[:-1])[len(prompt) - 1:]
+        for i, t in enumerate(toks):
+            assert ref[i, t] >= ref[i].max() - 2 * TOL_F32 * max(1.0, float(np.abs(ref).max())), (prompt, i)
+    # token by token through the same step function gives the same tokens
+    p2 = subprocess.run([c for c in cmd if c != "--random-weights"] + ["--no-prefill", "--quiet"], capture_output=True,
+                        text=True, timeout=600)
+    assert p2.returncode == 0, p2.stderr[-2000:]
+    assert [l for l in p2.stderr.splitlines() if l.startswith("token_id=")] == \
+           [l for l in p.stderr.splitlines() if l.startswith("token_id=")]
