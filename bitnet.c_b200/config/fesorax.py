@@ -33,7 +33,7 @@ from .spec import (BiasAttentionSpec, ConfigError, MlstmSpec, ModelSpec, MoeSpec
 
 ARCHITECTURE = "Fesorax"
 DEFAULT_MAX_POSITIONS = 1 << 20
-DEFAULT_BIAS_BUCKETS = 32
+DEFAULT_BIAS_BUCKETS = 64  # for configurations without a folder (random weights); a folder's tables say their own
 
 
 def _need(d: Dict[str, Any], key: str, where: str) -> Any:

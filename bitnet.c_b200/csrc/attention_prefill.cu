@@ -32,10 +32,11 @@ __device__ __forceinline__ unsigned tile_off(int row, int chunk) {
 // for designs that want their attention weights in single precision.
 __device__ __forceinline__ float bf16_rest(float p) { return p - __bfloat162float(__float2bfloat16_rn(p)); }
 
-template <int HD, bool PRECISE>
+// VD: the instantiation for the width of a value head (v_dim <= VD), which may differ from a key head's.
+template <int HD, bool PRECISE, int VD = HD>
 __global__ void __launch_bounds__(PF_THREADS)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
-                         int out_stride, int n_heads, int n_kv_heads, int head_dim, float scale_log2e, int window,
+                         int out_stride, int n_heads, int n_kv_heads, int head_dim, int v_dim, float scale_log2e, int window,
                          int keep_first, const float* __restrict__ rel, int n_rel,
                          const __nv_bfloat16* __restrict__ gate, int gate_stride,
                          const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
@@ -46,9 +47,11 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
   pdl_wait();               // the kernels before this one have completed and their writes are visible
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int TILE_BYTES = PF_N * HD * 2;
+  constexpr int VTILE_BYTES = PF_N * VD * 2;
   constexpr int CHUNKS = HD / 8;   // 16-byte chunks per row
+  constexpr int VCHUNKS = VD / 8;
   constexpr int KSTEPS = HD / 16;  // k-steps of the score product
-  constexpr int NT_O = HD / 8;     // 8-wide column tiles of the output
+  constexpr int NT_O = VD / 8;     // 8-wide column tiles of the output
   const unsigned s_q = (unsigned)__cvta_generic_to_shared(smem);
   const unsigned s_k = s_q + PF_M * HD * 2;      // two stages
   const unsigned s_v = s_k + 2 * TILE_BYTES;     // two stages
@@ -64,7 +67,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
   const int kvh = h / (n_heads / n_kv_heads);
   const int start = seq_start[seq], n_new = seq_start[seq + 1] - start, pos0 = seq_pos0[seq];
   const int* pt = page_table + (size_t)slots[seq] * pt_stride;
-  const int real_chunks = head_dim / 8;
+  const int real_chunks = head_dim / 8, real_vchunks = v_dim / 8;
   const int rows_here = min(PF_M, n_new - row0);
   const int seq_last = pos0 + n_new - 1;  // the last position of this sequence that the cache holds
 
@@ -87,16 +90,18 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
   auto load_kv = [&](int tile, int stage) {
     int page = pt[tile];
     const __nv_bfloat16* kb = k_cache + ((size_t)page * n_kv_heads + kvh) * BN_PAGE * head_dim;
-    const __nv_bfloat16* vb = v_cache + ((size_t)page * n_kv_heads + kvh) * BN_PAGE * head_dim;
+    const __nv_bfloat16* vb = v_cache + ((size_t)page * n_kv_heads + kvh) * BN_PAGE * v_dim;
     for (int p = tid; p < PF_N * CHUNKS; p += PF_THREADS) {
       int r = p / CHUNKS, c = p % CHUNKS;
       bool ok = c < real_chunks;
+      cp_async16(s_k + stage * TILE_BYTES + tile_off<HD>(r, c), ok ? kb + (size_t)r * head_dim + c * 8 : kb, ok);
+    }
+    for (int p = tid; p < PF_N * VCHUNKS; p += PF_THREADS) {
+      int r = p / VCHUNKS, c = p % VCHUNKS;
       // value rows behind the sequence's last position are zero here, whatever the cache holds:
       // their weights are zero, but zero times anything must be zero
-      bool okv = ok && tile * PF_N + r <= seq_last;
-      size_t off = (size_t)r * head_dim + c * 8;
-      cp_async16(s_k + stage * TILE_BYTES + tile_off<HD>(r, c), ok ? kb + off : kb, ok);
-      cp_async16(s_v + stage * TILE_BYTES + tile_off<HD>(r, c), okv ? vb + off : vb, okv);
+      bool okv = c < real_vchunks && tile * PF_N + r <= seq_last;
+      cp_async16(s_v + stage * VTILE_BYTES + tile_off<VD>(r, c), okv ? vb + (size_t)r * v_dim + c * 8 : vb, okv);
     }
   };
   load_kv(tile_of(0), 0);
@@ -136,7 +141,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     float s[PF_N / 8][4];
 #pragma unroll
     for (int j = 0; j < PF_N / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-    const unsigned kb = s_k + stage * TILE_BYTES, vb = s_v + stage * TILE_BYTES;
+    const unsigned kb = s_k + stage * TILE_BYTES, vb = s_v + stage * VTILE_BYTES;
 #pragma unroll
     for (int ks = 0; ks < KSTEPS; ++ks) {
       unsigned a0, a1, a2, a3;
@@ -220,7 +225,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
       for (int j = 0; j < NT_O; j += 2) {
         unsigned b0, b1, b2, b3;
         int mi = lane >> 3, r = lane & 7;
-        ldsm_x4_trans(vb + tile_off<HD>(ks * 16 + (mi & 1) * 8 + r, j + (mi >> 1)), b0, b1, b2, b3);
+        ldsm_x4_trans(vb + tile_off<VD>(ks * 16 + (mi & 1) * 8 + r, j + (mi >> 1)), b0, b1, b2, b3);
         mma_bf16(o[j], a0, a1, a2, a3, b0, b1);
         mma_bf16(o[j + 1], a0, a1, a2, a3, b2, b3);
         if (PRECISE) {
@@ -244,11 +249,11 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     if (r >= rows_here) continue;
     float inv = 1.0f / l_run[e];
     if (gate) inv *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)(start + row0 + r) * gate_stride + h])));
-    __nv_bfloat16* orow = out + (size_t)(start + row0 + r) * out_stride + (size_t)h * head_dim;
+    __nv_bfloat16* orow = out + (size_t)(start + row0 + r) * out_stride + (size_t)h * v_dim;
 #pragma unroll
     for (int j = 0; j < NT_O; ++j) {
       int d = j * 8 + 2 * t;
-      if (d < head_dim) {
+      if (d < v_dim) {
         __nv_bfloat162 v = __floats2bfloat162_rn(o[j][2 * e] * inv, o[j][2 * e + 1] * inv);
         *reinterpret_cast<__nv_bfloat162*>(orow + d) = v;
       }
@@ -256,25 +261,25 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
   }
 }
 
-template <int HD, bool PRECISE = false>
+template <int HD, bool PRECISE = false, int VD = HD>
 static int launch_prefill(const void* q, int q_stride, void* out, int out_stride, int n_tiles, int n_heads,
-                          int n_kv_heads, int head_dim, float scale, int window, int keep_first, const float* rel, int n_rel,
+                          int n_kv_heads, int head_dim, int v_dim, float scale, int window, int keep_first, const float* rel, int n_rel,
                           const void* gate, int gate_stride, const int* tile_seq,
                           const int* tile_row0, const int* seq_start, const int* seq_pos0, const int* slots,
                           const int* page_table, int pt_stride, const void* k_cache, const void* v_cache,
                           cudaStream_t stream) {
-  size_t smem = (size_t)PF_M * HD * 2 + 4 * (size_t)PF_N * HD * 2;
+  size_t smem = (size_t)PF_M * HD * 2 + 2 * (size_t)PF_N * HD * 2 + 2 * (size_t)PF_N * VD * 2;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD, PRECISE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD, PRECISE, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
     configured = true;
   }
   if (n_tiles > 65535) return BN_ERR_BAD_ARG;
   dim3 grid(n_heads, n_tiles);
-  BN_LAUNCH((attention_prefill_kernel<HD, PRECISE>), grid, PF_THREADS, smem, stream, 
-      (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, head_dim,
+  BN_LAUNCH((attention_prefill_kernel<HD, PRECISE, VD>), grid, PF_THREADS, smem, stream, 
+      (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, head_dim, v_dim,
       scale * 1.4426950408889634f, window, keep_first, rel, n_rel, (const __nv_bfloat16*)gate, gate_stride, tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table, pt_stride,
       (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache);
   BN_CHECK_LAUNCH();
@@ -289,7 +294,7 @@ static int launch_prefill(const void* q, int q_stride, void* out, int out_stride
 // one); gate [tokens, gate_stride] holds per token and head a number whose logistic function
 // multiplies the head's output.
 extern "C" int bn_attention_prefill_ex(const void* q, int q_stride, void* out, int out_stride, int n_tiles, int n_heads,
-                                       int n_kv_heads, int head_dim, float scale, int window, int keep_first,
+                                       int n_kv_heads, int head_dim, int v_dim, float scale, int window, int keep_first,
                                        const float* rel, int n_rel, const void* gate, int gate_stride, int precise,
                                        const int* tile_seq, const int* tile_row0, const int* seq_start,
                                        const int* seq_pos0, const int* slots, const int* page_table, int pt_stride,
@@ -297,15 +302,23 @@ extern "C" int bn_attention_prefill_ex(const void* q, int q_stride, void* out, i
   if (n_tiles <= 0) return BN_OK;
   if (head_dim <= 0 || head_dim % 16 || head_dim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads || window < 0 ||
       n_heads > 65535 || (q_stride % 8) || (out_stride % 2) || (((uintptr_t)q) & 15) || keep_first < 0 ||
-      (rel && n_rel <= 0))
+      (rel && n_rel <= 0) || v_dim <= 0 || v_dim % 16 || v_dim > 256 || (v_dim != head_dim && !precise))
     return BN_ERR_BAD_ARG;
-#define BN_PF_ARGS q, q_stride, out, out_stride, n_tiles, n_heads, n_kv_heads, head_dim, scale, window, keep_first, rel, \
+#define BN_PF_ARGS q, q_stride, out, out_stride, n_tiles, n_heads, n_kv_heads, head_dim, v_dim, scale, window, keep_first, rel, \
                    n_rel, gate, gate_stride, tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table, pt_stride,      \
                    k_cache, v_cache, stream
   if (precise) {
-    if (head_dim <= 64) return launch_prefill<64, true>(BN_PF_ARGS);
-    if (head_dim <= 128) return launch_prefill<128, true>(BN_PF_ARGS);
-    return launch_prefill<256, true>(BN_PF_ARGS);
+    // key and value heads of their own widths: the instantiation for each
+    const int hd = head_dim <= 64 ? 64 : head_dim <= 128 ? 128 : 256, vd = v_dim <= 64 ? 64 : v_dim <= 128 ? 128 : 256;
+    if (hd == 64 && vd == 64) return launch_prefill<64, true, 64>(BN_PF_ARGS);
+    if (hd == 64 && vd == 128) return launch_prefill<64, true, 128>(BN_PF_ARGS);
+    if (hd == 64) return launch_prefill<64, true, 256>(BN_PF_ARGS);
+    if (hd == 128 && vd == 64) return launch_prefill<128, true, 64>(BN_PF_ARGS);
+    if (hd == 128 && vd == 128) return launch_prefill<128, true, 128>(BN_PF_ARGS);
+    if (hd == 128) return launch_prefill<128, true, 256>(BN_PF_ARGS);
+    if (vd == 64) return launch_prefill<256, true, 64>(BN_PF_ARGS);
+    if (vd == 128) return launch_prefill<256, true, 128>(BN_PF_ARGS);
+    return launch_prefill<256, true, 256>(BN_PF_ARGS);
   }
   if (head_dim <= 64) return launch_prefill<64>(BN_PF_ARGS);
   if (head_dim <= 128) return launch_prefill<128>(BN_PF_ARGS);
@@ -318,7 +331,7 @@ extern "C" int bn_attention_prefill(const void* q, int q_stride, void* out, int 
                                     const int* tile_row0, const int* seq_start, const int* seq_pos0,
                                     const int* slots, const int* page_table, int pt_stride, const void* k_cache,
                                     const void* v_cache, cudaStream_t stream) {
-  return bn_attention_prefill_ex(q, q_stride, out, out_stride, n_tiles, n_heads, n_kv_heads, head_dim, scale, window, 0,
+  return bn_attention_prefill_ex(q, q_stride, out, out_stride, n_tiles, n_heads, n_kv_heads, head_dim, head_dim, scale, window, 0,
                                  nullptr, 0, nullptr, 0, 0, tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table,
                                  pt_stride, k_cache, v_cache, stream);
 }

@@ -358,7 +358,7 @@ def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_heads
                       precise: bool = False) -> torch.Tensor:
     """bfloat16 causal attention of runs of new tokens on the tensor cores; block i handles up to 64
     new tokens of sequence tile_seq[i] from its row tile_row0[i] on.  ``keep_first``, ``rel`` and ``gate`` as
-    for ``attention_general``; ``precise``: the softmax weights enter the second product with 16 bits of
+    for ``attention_general``; a value head may have a width of its own (``v_cache``'s rows; with ``precise``); ``precise``: the softmax weights enter the second product with 16 bits of
     mantissa (as two bfloat16 terms) instead of 8."""
     if not q.is_cuda or q.stride(-1) != 1 or q.dtype != torch.bfloat16:
         raise KernelError("attention_prefill: q must be a bfloat16 CUDA tensor with unit inner stride")
@@ -369,11 +369,15 @@ def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_heads
     _need(page_table, "page_table", torch.int32, 2)
     _need(k_cache, "k_cache", torch.bfloat16, 4)
     _need(v_cache, "v_cache", torch.bfloat16, 4)
-    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or k_cache.shape != v_cache.shape:
-        raise KernelError(f"attention_prefill: cache {tuple(k_cache.shape)} is not [pages, {n_kv_heads}, {PAGE}, {head_dim}]")
-    if head_dim % 16 or head_dim > 256 or n_heads % n_kv_heads:
-        raise KernelError(f"attention_prefill: head_dim={head_dim}, heads {n_heads}/{n_kv_heads} not supported")
-    if out.shape[1] != n_heads * head_dim or q_stride % 8:
+    v_dim = v_cache.shape[3]
+    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or tuple(k_cache.shape[:3]) != tuple(v_cache.shape[:3]):
+        raise KernelError(f"attention_prefill: cache {tuple(k_cache.shape)} / {tuple(v_cache.shape)} is not "
+                          f"[pages, {n_kv_heads}, {PAGE}, {head_dim} / value width]")
+    if head_dim % 16 or head_dim > 256 or n_heads % n_kv_heads or v_dim % 16 or v_dim > 256:
+        raise KernelError(f"attention_prefill: head_dim={head_dim}, value width {v_dim}, heads {n_heads}/{n_kv_heads} not supported")
+    if v_dim != head_dim and not precise:
+        raise KernelError("attention_prefill: a value width of its own is built for precise weights only")
+    if out.shape[1] != n_heads * v_dim or q_stride % 8:
         raise KernelError("attention_prefill: out or q_stride does not fit")
     n_rel = 0
     if rel is not None:
@@ -387,7 +391,7 @@ def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_heads
     if keep_first or rel is not None or gate is not None or precise:
         _check(_fn("attention_prefill", "bn_attention_prefill_ex")(
             _ptr(q), int(q_stride), _ptr(out), int(out.shape[1]), int(tile_seq.shape[0]), int(n_heads),
-            int(n_kv_heads), int(head_dim), c_float(scale), int(window), int(keep_first), _ptr(rel), int(n_rel), _ptr(gate),
+            int(n_kv_heads), int(head_dim), int(v_dim), c_float(scale), int(window), int(keep_first), _ptr(rel), int(n_rel), _ptr(gate),
             int(gate_stride), int(bool(precise)), _ptr(tile_seq), _ptr(tile_row0), _ptr(seq_start), _ptr(seq_pos0), _ptr(slots),
             _ptr(page_table), int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), _stream()), "attention_prefill")
         return out

@@ -122,7 +122,7 @@ class BiasAttention(Mixer):
         gate = proj[:, self.g_off:] if s.head_gate else None
         keep = s.keep_first if s.window > 0 else 0
         if (self.build.dtype == torch.bfloat16 and not ctx.decode and ctx.tile_seq is not None and ctx.max_new >= self.TILED_MIN_TOKENS
-                and s.v_head_dim == s.head_dim and s.head_dim % 16 == 0):
+                and s.v_head_dim % 16 == 0 and s.head_dim % 16 == 0):
             # runs of new tokens: 64 tokens of a sequence and a head per block on the tensor cores, the
             # softmax weights with 16 bits of mantissa
             ops.attention_prefill(proj, self.row, out, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, ctx.tile_seq,
