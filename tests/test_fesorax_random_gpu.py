@@ -19,7 +19,7 @@ def draw_config(seed: int):
     pick = lambda xs: xs[int(rng.integers(len(xs)))]
     width = pick([32, 48, 64, 72, 96, 128])
     layers, rel_rows, owners = [], {}, []
-    for i in range(int(rng.integers(1, 6))):
+    for i in range(int(rng.integers(1, 8))):
         if rng.random() < 0.6:
             src = pick(owners) if owners and rng.random() < 0.4 else None
             if src is not None:
