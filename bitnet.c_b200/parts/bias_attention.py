@@ -43,8 +43,6 @@ class BiasAttention(Mixer):
             raise ValueError(f"{spec.n_heads} heads are not a multiple of {spec.n_kv_heads} key/value heads")
         if not 0 < spec.head_dim <= 256 or not 0 < spec.v_head_dim <= 256:
             raise ValueError(f"head_dim={spec.head_dim} and v_head_dim={spec.v_head_dim} must be at most 256")
-        if not spec.unit_norm:
-            raise ValueError("this mixer is built with unit-norm queries and keys only")
         self.w_in: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
         self.rel: Optional[torch.Tensor] = None
@@ -110,7 +108,10 @@ class BiasAttention(Mixer):
         if kv.owner != s.own_kv:
             raise ValueError("a mixer with key/value projections owns its cache plane, one without reads another's")
         proj = ops.linear(h, self.w_in, out_dtype=self.build.dtype)
-        if kv.owner:
+        if not s.unit_norm:
+            if kv.owner:  # queries and keys as the projections gave them
+                kv.append(proj, self.k_off, self.v_off, ctx)
+        elif kv.owner:
             ops.unit_norm_append(proj, s.n_heads, s.head_dim, s.norm_eps, ctx.tok_pos, k_off=self.k_off, v_off=self.v_off,
                                  n_kv_heads=s.n_kv_heads, tok_seq=ctx.tok_seq, slots=ctx.slots, page_table=kv.page_table,
                                  k_cache=kv.k, v_cache=kv.v)
