@@ -123,8 +123,9 @@ class FesoraxConfig:
                 raise ConfigError(f"config.json: {where}.kv_from={src}: that layer has no keys and values of its own")
             if (om.get("kv_heads"), om.get("dim"), om.get("vdim")) != (kv_heads, dim, m.get("vdim")):
                 raise ConfigError(f"config.json: {where}.kv_from={src}: the two layers' kv_heads, dim and vdim differ")
-        buckets = int(m.get("bias_buckets") or DEFAULT_BIAS_BUCKETS)
         bias_max = _int(m, "bias_max", where)
+        # without tables to read the number of rows from: the default, or fewer where the bias reaches less far
+        buckets = int(m.get("bias_buckets") or max(2, min(DEFAULT_BIAS_BUCKETS, 2 * (bias_max - 1))))
         if bias_max <= buckets // 2:
             raise ConfigError(f"config.json: {where}.bias_max={bias_max} must exceed half the {buckets} distance buckets")
         return BiasAttentionSpec(

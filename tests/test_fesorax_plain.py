@@ -136,7 +136,8 @@ def test_a_windowed_cache_keeps_the_first_pages_and_what_its_readers_see():
     import bitnet_c_b200 as bn
     from bitnet_c_b200.config import architecture_of
     arch = architecture_of(fc.CASE_B)
-    model = bn.Model(arch.to_spec(arch.read_config(fc.CASE_B)), dtype="float32", device=None)
+    cfg = arch.read_config(arch.complete_config(fc.CASE_B, fc.tensor_shapes(fc.CASE_B, fc.REL_ROWS_B)))
+    model = bn.Model(arch.to_spec(cfg), dtype="float32", device=None)
     cache = model.new_cache(max_tokens=64 * 40, allocate=False)
     # layer 2 reads layer 0's plane with a window of 1000: the plane keeps that, and the 70 first positions
     (g,) = cache.groups
