@@ -287,7 +287,7 @@ extern "C" int bn_mlstm_recurrence(const void* qkv, int dtype, int row_stride, i
 // head, 32 value columns); the 32 tokens of a chunk are the 32 lanes of a warp for the scans.
 // The sums run in another order than token by token, so the two forms agree to rounding, not bit by bit.
 #define MLC_L 32
-#define MLC_THREADS 256
+#define MLC_THREADS 512
 #define MLC_ROWS (MLC_L / (MLC_THREADS / 32))  // rows of a chunk per warp
 
 template <typename T>
@@ -324,7 +324,7 @@ __global__ void __launch_bounds__(MLC_THREADS) mlstm_chunk_kernel(
   // Rows of whole 16-byte pieces (the usual case) are read in such pieces, and a chunk's q and k rows are
   // requested into registers while the chunk before is worked on; other sizes go number by number.
   constexpr int VN = 16 / sizeof(T);
-  constexpr int MAXV = 4;  // pieces per thread and matrix: 32 rows of up to 128 numbers in float32, 256 in bfloat16
+  constexpr int MAXV = 2;  // pieces per thread and matrix: 32 rows of up to 128 numbers in float32, 256 in bfloat16
   const bool wide = dim % VN == 0 && k_off % VN == 0 && row_stride % VN == 0 && v_off % VN == 0 && vdim % VN == 0 &&
                     (((uintptr_t)qkv) & 15) == 0 && MLC_L * dim / VN <= MAXV * MLC_THREADS;
   const int pieces = wide ? MLC_L * dim / VN : 0, per_row = wide ? dim / VN : 1;
@@ -415,20 +415,22 @@ __global__ void __launch_bounds__(MLC_THREADS) mlstm_chunk_kernel(
     const float m_end = __shfl_sync(0xffffffffu, m_tok, n_tok - 1);
     if (warp == 0) s_g[lane] = g_state;
     __syncthreads();  // sQ, sK, sV, s_g are loaded
-    // ---- P[t][s] = (q_t . k_s) e^{z_s - M_t} for s <= t: thread = (row t, columns s = (tid & 7) + 8 j), so that
-    // the eight threads of a row read eight neighbouring rows of K (rows lie dim + 4 numbers apart: no two in one bank)
+    // ---- P[t][s] = (q_t . k_s) e^{z_s - M_t} for s <= t: thread = (row t, columns s = s0 + TPR j), so that
+    // the threads of a row read neighbouring rows of K (rows lie dim + 4 numbers apart: no two in one bank)
     {
-      const int t = tid >> 3, s0 = tid & 7;
-      float acc[4];
+      constexpr int TPR = MLC_THREADS / MLC_L;  // threads per row
+      constexpr int CPT = MLC_L / TPR;          // columns per thread
+      const int t = tid / TPR, s0 = tid % TPR;
+      float acc[CPT];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) acc[j] = 0.f;
-      const int n_col = (t - s0 + 8) >> 3;  // how many of this thread's columns lie at or below the diagonal
+      for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
+      const int n_col = (t - s0 + TPR) / TPR;  // how many of this thread's columns lie at or below the diagonal
       for (int d = 0; d < dim; d += 4) {
         float4 q4 = *reinterpret_cast<const float4*>(sQ + t * ld + d);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < CPT; ++j) {
           if (j < n_col) {
-            float4 k4 = *reinterpret_cast<const float4*>(sK + (s0 + 8 * j) * ld + d);
+            float4 k4 = *reinterpret_cast<const float4*>(sK + (s0 + TPR * j) * ld + d);
             acc[j] = fmaf(q4.x, k4.x, acc[j]); acc[j] = fmaf(q4.y, k4.y, acc[j]);
             acc[j] = fmaf(q4.z, k4.z, acc[j]); acc[j] = fmaf(q4.w, k4.w, acc[j]);
           }
@@ -436,8 +438,8 @@ __global__ void __launch_bounds__(MLC_THREADS) mlstm_chunk_kernel(
       }
       const float M_t = __shfl_sync(0xffffffffu, M, t);  // every warp holds all tokens' scalars, lane = token
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        int sidx = s0 + 8 * j;
+      for (int j = 0; j < CPT; ++j) {
+        int sidx = s0 + TPR * j;
         float z_s = __shfl_sync(0xffffffffu, z, sidx);
         sP[t * (MLC_L + 1) + sidx] = (sidx <= t && sidx < n_tok) ? acc[j] * expf(z_s - M_t) : 0.f;
       }
@@ -486,15 +488,15 @@ __global__ void __launch_bounds__(MLC_THREADS) mlstm_chunk_kernel(
       }
     }
     __syncthreads();  // everyone has read sS and sn as they were before the chunk
-    // ---- the state after the chunk: thread = (column, sixteen rows d at a time; the warps take turns)
-    for (int dbase = warp * 16; dbase < dim; dbase += 16 * (MLC_THREADS / 32)) {
-      float acc[16];
+    // ---- the state after the chunk: thread = (column, eight rows d at a time; the warps take turns)
+    for (int dbase = warp * 8; dbase < dim; dbase += 8 * (MLC_THREADS / 32)) {
+      float acc[8];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
       for (int sidx = 0; sidx < n_tok; ++sidx) {
         const float gv = s_g[sidx] * sV[sidx * 32 + lane];
 #pragma unroll
-        for (int j = 0; j < 16; j += 4) {
+        for (int j = 0; j < 8; j += 4) {
           // rows are padded by four and followed by other arrays: a read past dim stays inside and is not kept
           float4 k4 = *reinterpret_cast<const float4*>(sK + sidx * ld + dbase + j);
           acc[j] = fmaf(gv, k4.x, acc[j]);         acc[j + 1] = fmaf(gv, k4.y, acc[j + 1]);
@@ -502,7 +504,7 @@ __global__ void __launch_bounds__(MLC_THREADS) mlstm_chunk_kernel(
         }
       }
 #pragma unroll
-      for (int j = 0; j < 16; ++j)
+      for (int j = 0; j < 8; ++j)
         if (dbase + j < dim) sS[(dbase + j) * 32 + lane] = fmaf(carry_last, sS[(dbase + j) * 32 + lane], acc[j]);
     }
     for (int d = tid; d < dim; d += MLC_THREADS) {
