@@ -36,7 +36,7 @@ class KvView:
     """What a mixer sees of the cache for one run."""
 
     k: torch.Tensor  # [pages, kv_heads, PAGE, head_dim]
-    v: torch.Tensor  # [pages, kv_heads, PAGE, v_head_dim]
+    v: Optional[torch.Tensor]  # [pages, kv_heads, PAGE, v_head_dim]; None: the values are a part of the key rows
     page_table: torch.Tensor  # [slots, pages_per_sequence] int32
     n_kv_heads: int
     head_dim: int
@@ -82,13 +82,14 @@ class KvGroup:
         shape = (len(entries), n_pages, request.n_kv_heads, PAGE, request.head_dim)
         if allocate:
             self.k = torch.zeros(shape, dtype=dtype, device=device)
-            self.v = torch.zeros(shape[:-1] + (request.v_dim,), dtype=dtype, device=device)
+            self.v = None if request.values_in_keys else torch.zeros(shape[:-1] + (request.v_dim,), dtype=dtype, device=device)
             self.page_table = torch.zeros((n_slots, pages_per_seq), dtype=torch.int32, device=device)
         else:  # bookkeeping only (tests without a device)
             self.k = self.v = self.page_table = None
 
     def bytes_per_token(self, itemsize: int) -> int:
-        return len(self.entries) * self.request.n_kv_heads * (self.request.head_dim + self.request.v_dim) * itemsize
+        per_head = self.request.head_dim + (0 if self.request.values_in_keys else self.request.v_dim)
+        return len(self.entries) * self.request.n_kv_heads * per_head * itemsize
 
     def reserve(self, slot: int, old_len: int, new_len: int) -> None:
         """Hold pages for positions [first needed, new_len)."""
@@ -100,6 +101,9 @@ class KvGroup:
         if self.request.window > 0:
             # the oldest key any new token needs: position old_len - window + 1
             first = max(0, old_len - self.request.window + 1) // PAGE
+        elif self.request.chunk > 0:
+            # the first new token sees back to the start of its own chunk, later ones no further
+            first = (old_len // self.request.chunk) * self.request.chunk // PAGE
         # (with ``keep_first`` the first pages were taken when the sequence began and are never given back)
         need = [i for i in range(first, pages_for(new_len)) if i not in held]
         if need and need[-1] >= self.pages_per_seq:
@@ -114,10 +118,13 @@ class KvGroup:
 
     def trim(self, slot: int, length: int) -> None:
         """Give back pages that lie wholly before the window of a sequence of ``length`` tokens."""
-        if self.request.window <= 0:
+        if self.request.window <= 0 and self.request.chunk <= 0:
             return
         held = self.held.get(slot, {})
-        first_needed = max(0, length - self.request.window + 1) // PAGE
+        if self.request.chunk > 0:  # the next token sees back to the start of its chunk
+            first_needed = (length // self.request.chunk) * self.request.chunk // PAGE
+        else:
+            first_needed = max(0, length - self.request.window + 1) // PAGE
         kept = pages_for(self.request.keep_first)  # the pages of the first positions stay
         gone = [i for i in held if kept <= i < first_needed]
         self.pool.free([held.pop(i) for i in gone])
@@ -170,7 +177,7 @@ class Cache:
         for req, entries in by_request.items():
             # a windowed plane holds only part of a sequence, so a sequence may be longer than the pool:
             # its page table reaches as far as the context does (at least 1,024 pages)
-            per_seq = min(pages_for(max_positions), max(n_pages, 1024)) if req.window > 0 else pages_per_seq
+            per_seq = min(pages_for(max_positions), max(n_pages, 1024)) if (req.window > 0 or req.chunk > 0) else pages_per_seq
             g = KvGroup(req, entries, n_pages, n_slots, per_seq, dtype, device, allocate)
             for plane, e in enumerate(entries):
                 self._plane[e] = (len(self.groups), plane)
@@ -261,7 +268,7 @@ class Cache:
             return None
         gi, plane = self._plane[src]
         g = self.groups[gi]
-        return KvView(k=g.k[plane], v=g.v[plane], page_table=g.page_table, n_kv_heads=g.request.n_kv_heads,
+        return KvView(k=g.k[plane], v=g.v[plane] if g.v is not None else None, page_table=g.page_table, n_kv_heads=g.request.n_kv_heads,
                       head_dim=g.request.head_dim, window=g.request.window, owner=owner,
                       v_head_dim=g.request.v_head_dim)
 

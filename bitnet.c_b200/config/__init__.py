@@ -1,5 +1,6 @@
 """Typed configuration, the block-by-block model description, and the architecture registry."""
 from .spec import (BiasAttentionSpec, MlstmSpec, MoeSpec, PostNormBlockSpec)  # noqa: F401
+from .spec import (DeltaRuleSpec, LatentAttentionSpec, ParallelBlockSpec, RotaryPairsSpec, TokenSideSpec)  # noqa: F401
 from .spec import (AttentionSpec, BlockSpec, ConfigError, GatedMlpSpec, LinearHeadSpec, ModelSpec, NoPositionSpec,
                    RmsNormSpec, RotarySpec, ScheduleEntry)
 from .registry import (Architecture, architecture, architecture_of, known_architectures,
@@ -29,9 +30,23 @@ register_architecture(Architecture(
     complete_config=_fesorax.with_sizes_of,
 ))
 
+from . import lotilix as _lotilix
+from .lotilix import LotilixConfig
+
+register_architecture(Architecture(
+    name=_lotilix.ARCHITECTURE,
+    read_config=LotilixConfig.from_dict,
+    to_spec=LotilixConfig.to_spec,
+    tensor_name=_lotilix.tensor_name,
+    cap_positions=LotilixConfig.with_max_positions,
+    config_to_dict=LotilixConfig.to_dict,
+    complete_config=_lotilix.with_sizes_of,
+))
+
 __all__ = [
     "AttentionSpec", "BlockSpec", "ConfigError", "GatedMlpSpec", "LinearHeadSpec", "ModelSpec", "NoPositionSpec",
     "RmsNormSpec", "RotarySpec", "ScheduleEntry", "Architecture", "architecture", "architecture_of",
     "known_architectures", "read_config_json", "register_architecture", "unregister_architecture",
     "LlamaConfig", "FesoraxConfig", "BiasAttentionSpec", "MlstmSpec", "MoeSpec", "PostNormBlockSpec",
+    "LotilixConfig", "DeltaRuleSpec", "LatentAttentionSpec", "ParallelBlockSpec", "RotaryPairsSpec", "TokenSideSpec",
 ]

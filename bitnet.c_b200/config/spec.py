@@ -44,6 +44,18 @@ class RotarySpec:
 
 
 @dataclass(frozen=True)
+class RotaryPairsSpec:
+    """Rotary position encoding in the interleaved pairing (2i, 2i + 1): the pair i of the rotated part is turned
+    by position * base^(-2i/dims).  ``scaling`` = (factor, low, high, original) slows long wavelengths down:
+    beyond original / low by ``factor``, between original / high and original / low by a blend of both."""
+
+    dims: int
+    base: float
+    scaling: Optional[Tuple[float, float, float, float]] = None
+    kind: str = "rotary_pairs"
+
+
+@dataclass(frozen=True)
 class NoPositionSpec:
     """No position encoding at all."""
 
@@ -97,7 +109,50 @@ class BiasAttentionSpec:
     bias_max_distance: int = 0  # the distance from which on the last bucket is used
     head_gate: bool = False  # one gate per head from the mixer's input
     own_kv: bool = True  # False: no key/value projections; the run reads another run's cache
+    chunk: int = 0  # c > 0 (in place of a window): a token sees the earlier keys of its own chunk of c positions
+    position: Any = None  # a position spec whose encoding q and k get (after the unit norm, if any); None: none
+    values_are_keys: bool = False  # no value projection: the values are the keys as projected, before any encoding
     kind: str = "bias_attention"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Softmax attention through low-rank latents: queries from a normed latent of ``q_rank`` numbers; per token
+    one normed latent of ``kv_rank`` numbers, from which every head's unrotated keys (``head_dim``) and values
+    (``v_head_dim``) come, and one rotated key part of ``rot_dim`` numbers that all heads share.  Only the latent
+    and the rotated part are cached.  ``window``: the last so many keys (0: all); a logistic gate per head."""
+
+    width: int
+    n_heads: int
+    head_dim: int
+    rot_dim: int
+    v_head_dim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    position: Any  # the encoding of the rotated parts (dims = rot_dim)
+    norm_eps: float
+    window: int = 0
+    head_gate: bool = True
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class DeltaRuleSpec:
+    """Gated delta rule with one decay per head and key channel: short causal convolutions and SiLU on q, k, v;
+    unit q and k; beta and the decays from the mixer's input (the decays through ``decay_rank`` numbers); a
+    per-head unit norm with a shared gain and a logistic gate (through ``gate_rank`` numbers) on the output."""
+
+    width: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    v_head_dim: int
+    conv_taps: int
+    decay_rank: int
+    gate_rank: int
+    norm_eps: float
+    kind: str = "delta_rule"
 
 
 @dataclass(frozen=True)
@@ -137,7 +192,8 @@ class GatedMlpSpec:
 
     width: int
     intermediate: int
-    activation: str = "silu"
+    activation: str = "silu"  # or "gelu_tanh"
+    wide_output: bool = False  # the delta leaves the last product in float32 instead of the compute type
     kind: str = "gated_mlp"
 
 
@@ -163,6 +219,34 @@ class PostNormBlockSpec:
     ffn_norm: Any
     alpha: float = 1.0
     kind: str = "post_norm"
+
+
+@dataclass(frozen=True)
+class TokenSideSpec:
+    """A small input by token id at the end of a block: e = table[token, column : column + dim];
+    y = proj (act(gate x) * e); x <- x + y / rms(y) * gain.  ``table_width``: the row of the table, which the
+    blocks of a model share, each with its own columns."""
+
+    width: int
+    vocab_size: int
+    dim: int
+    column: int
+    table_width: int
+    eps: float
+    activation: str = "gelu_tanh"
+    kind: str = "token_side"
+
+
+@dataclass(frozen=True)
+class ParallelBlockSpec:
+    """A block with one norm whose output both sublayers read: x <- x + (mixer(norm(x)) + ffn(norm(x))); then
+    ``side`` (optional), which adds an input of its own.  ``ffn`` may be None."""
+
+    mixer: Any
+    ffn: Any
+    norm: Any
+    side: Any = None
+    kind: str = "parallel"
 
 
 @dataclass(frozen=True)

@@ -7,10 +7,10 @@
 // path (src/transformer/cpu_backend.c:365-392, src/transformer/prefill_backend.c:25-49).
 #include "common.cuh"
 
-__device__ __forceinline__ float silu_mul_one(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+__device__ __forceinline__ float glu_mul_one(float g, float u, int act) { return glu_activation(g, act) * u; }
 
 __global__ void silu_mul_bf16_kernel(const __nv_bfloat16* __restrict__ h, __nv_bfloat16* __restrict__ out,
-                                     int blocks_per_row, size_t total_blocks) {
+                                     int blocks_per_row, size_t total_blocks, int act) {
   pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
   pdl_wait();               // the kernels before this one have completed and their writes are visible
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -26,13 +26,13 @@ __global__ void silu_mul_bf16_kernel(const __nv_bfloat16* __restrict__ h, __nv_b
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     float2 g = __bfloat1622float2(g2[i]), u = __bfloat1622float2(u2[i]);
-    r2[i] = __floats2bfloat162_rn(silu_mul_one(g.x, u.x), silu_mul_one(g.y, u.y));
+    r2[i] = __floats2bfloat162_rn(glu_mul_one(g.x, u.x, act), glu_mul_one(g.y, u.y, act));
   }
   *reinterpret_cast<uint4*>(out + (t * blocks_per_row + j) * 8) = res;
 }
 
 __global__ void silu_mul_f32_kernel(const float* __restrict__ h, float* __restrict__ out, int blocks_per_row,
-                                    size_t total_blocks) {
+                                    size_t total_blocks, int act) {
   pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
   pdl_wait();               // the kernels before this one have completed and their writes are visible
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -42,24 +42,30 @@ __global__ void silu_mul_f32_kernel(const float* __restrict__ h, float* __restri
   const float4* src = reinterpret_cast<const float4*>(h + (t * blocks_per_row + j) * 16);
   float4 g0 = src[0], g1 = src[1], u0 = src[2], u1 = src[3];
   float4* dst = reinterpret_cast<float4*>(out + (t * blocks_per_row + j) * 8);
-  dst[0] = make_float4(silu_mul_one(g0.x, u0.x), silu_mul_one(g0.y, u0.y), silu_mul_one(g0.z, u0.z), silu_mul_one(g0.w, u0.w));
-  dst[1] = make_float4(silu_mul_one(g1.x, u1.x), silu_mul_one(g1.y, u1.y), silu_mul_one(g1.z, u1.z), silu_mul_one(g1.w, u1.w));
+  dst[0] = make_float4(glu_mul_one(g0.x, u0.x, act), glu_mul_one(g0.y, u0.y, act), glu_mul_one(g0.z, u0.z, act), glu_mul_one(g0.w, u0.w, act));
+  dst[1] = make_float4(glu_mul_one(g1.x, u1.x, act), glu_mul_one(g1.y, u1.y, act), glu_mul_one(g1.z, u1.z, act), glu_mul_one(g1.w, u1.w, act));
 }
 
 // h: [n_rows, 2 * inter], out: [n_rows, inter]; inter a multiple of 8, both 16-byte aligned.
-extern "C" int bn_silu_mul(const void* h, void* out, int dtype, int n_rows, int inter, cudaStream_t stream) {
+// act: the gate's activation (BN_ACT_SILU, BN_ACT_GELU_TANH)
+extern "C" int bn_glu_mul(const void* h, void* out, int dtype, int n_rows, int inter, int act, cudaStream_t stream) {
   if (n_rows <= 0) return BN_OK;
+  if (act != BN_ACT_SILU && act != BN_ACT_GELU_TANH) return BN_ERR_BAD_ARG;
   if (inter <= 0 || inter % 8 || (((uintptr_t)h | (uintptr_t)out) & 15)) return BN_ERR_BAD_ARG;
   int bpr = inter / 8;
   size_t total = (size_t)n_rows * bpr;
   unsigned blocks = (unsigned)((total + 255) / 256);
   if (dtype == BN_F32)
-    BN_LAUNCH(silu_mul_f32_kernel, blocks, 256, 0, stream, (const float*)h, (float*)out, bpr, total);
+    BN_LAUNCH(silu_mul_f32_kernel, blocks, 256, 0, stream, (const float*)h, (float*)out, bpr, total, act);
   else if (dtype == BN_BF16)
-    BN_LAUNCH(silu_mul_bf16_kernel, blocks, 256, 0, stream, (const __nv_bfloat16*)h, (__nv_bfloat16*)out, bpr, total);
+    BN_LAUNCH(silu_mul_bf16_kernel, blocks, 256, 0, stream, (const __nv_bfloat16*)h, (__nv_bfloat16*)out, bpr, total, act);
   else
     return BN_ERR_BAD_ARG;
   return BN_OK;
+}
+
+extern "C" int bn_silu_mul(const void* h, void* out, int dtype, int n_rows, int inter, cudaStream_t stream) {
+  return bn_glu_mul(h, out, dtype, n_rows, inter, BN_ACT_SILU, stream);
 }
 
 // x = x * scale, then (cap != 0) x = tanhf(x / cap) * cap: an output head's logit scale and the
@@ -141,5 +147,36 @@ extern "C" int bn_glu_limited(const void* h, void* out, int dtype, int n_rows, i
               inter, total, limit, slope);
   else
     return BN_ERR_BAD_ARG;
+  return BN_OK;
+}
+
+// A gated row of a second embedding: out[t, j] = act(pre[t, j]) * table[tokens[t], col0 + j], j < dim.
+// pre [n, pre_stride] and out [n, dim] of type `dtype`; the table [vocab, table_stride] of type
+// `table_dtype`; an id outside the table gives zeros.
+__global__ void gated_lookup_kernel(const void* __restrict__ pre, int pre_stride, int dtype, const void* __restrict__ table,
+                                    int table_dtype, int table_stride, int col0, int vocab, const int* __restrict__ tokens,
+                                    void* __restrict__ out, int dim, size_t total, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  size_t t = idx / dim;
+  int j = (int)(idx - t * dim);
+  int tok = tokens[t];
+  float e = (tok >= 0 && tok < vocab) ? load_as_f32(table, table_dtype, (size_t)tok * table_stride + col0 + j) : 0.f;
+  store_from_f32(out, dtype, idx, glu_activation(load_as_f32(pre, dtype, t * pre_stride + j), act) * e);
+}
+
+extern "C" int bn_gated_lookup(const void* pre, int pre_stride, int dtype, const void* table, int table_dtype,
+                               int table_stride, int col0, int vocab, const int* tokens, void* out, int n, int dim, int act,
+                               cudaStream_t stream) {
+  if (n <= 0) return BN_OK;
+  if (dim <= 0 || col0 < 0 || col0 + dim > table_stride || pre_stride < dim || !pre || !table || !tokens || !out ||
+      (dtype != BN_F32 && dtype != BN_BF16) || (table_dtype != BN_F32 && table_dtype != BN_BF16) ||
+      (act != BN_ACT_SILU && act != BN_ACT_GELU_TANH))
+    return BN_ERR_BAD_ARG;
+  size_t total = (size_t)n * dim;
+  BN_LAUNCH(gated_lookup_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, pre, pre_stride, dtype, table, table_dtype,
+            table_stride, col0, vocab, tokens, out, dim, total, act);
   return BN_OK;
 }

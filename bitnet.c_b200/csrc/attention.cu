@@ -45,11 +45,15 @@ struct Vec16<__nv_bfloat16> {
 //   rel, n_rel   additive bias by distance, rel[min(pos - p, n_rel - 1) * n_heads + h] (float32; the
 //                scale does not multiply it)
 //   gate         per token and head a number whose logistic function multiplies the head's output
+//   chunk        positions are cut into chunks of this many and a token sees the earlier keys of its own
+//                chunk only (takes the place of the window)
+//   v_row        width of a row of the value plane when it is more than v_dim: the values are the first
+//                v_dim numbers of each row (the key plane itself, for values that are a part of the keys)
 template <typename T>
 __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out,
                                          int out_stride, int n_heads, int n_kv_heads, int head_dim, int v_dim,
-                                         float scale, int window, int keep_first, const float* __restrict__ rel,
-                                         int n_rel, const T* __restrict__ gate, int gate_stride,
+                                         float scale, int window, int keep_first, int chunk, int v_row,
+                                         const float* __restrict__ rel, int n_rel, const T* __restrict__ gate, int gate_stride,
                                          const int* __restrict__ tok_seq,
                                          const int* __restrict__ tok_pos, const int* __restrict__ slots,
                                          const int* __restrict__ page_table, int pt_stride,
@@ -65,7 +69,7 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
   int kvh = h / (n_heads / n_kv_heads);
   int pos = tok_pos[t];
   const int* pt = page_table + (size_t)slots[tok_seq[t]] * pt_stride;
-  int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  int lo = chunk > 0 ? (pos / chunk) * chunk : (window > 0 ? max(0, pos - window + 1) : 0);
   // visible keys: positions [0, n_first) and [lo, pos]; u counts through both ranges
   int n_first = min(keep_first, lo);
   int n_keys = n_first + pos - lo + 1;
@@ -79,7 +83,7 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
   // Weighted sum of the values.  Rows of whole 16-byte pieces: a row is read by v_dim / VN threads,
   // one piece each, and the rows of a chunk are shared out over the groups of such threads; the
   // groups' sums meet in shared memory at the end.  Other widths: one thread per dimension.
-  const bool wide = (v_dim % VN) == 0 && v_dim / VN <= ATT_THREADS;
+  const bool wide = (v_dim % VN) == 0 && (v_row % VN) == 0 && v_dim / VN <= ATT_THREADS;
   const int per_row = wide ? v_dim / VN : 1, groups = wide ? ATT_THREADS / per_row : 1;
   const int piece = threadIdx.x % per_row, group = threadIdx.x / per_row;
   float acc[MAX_D] = {0.f, 0.f};
@@ -127,7 +131,7 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
           int u = base + j;
           int p = u < n_first ? u : lo + (u - n_first);
           float vv[VN];
-          Vec16<T>::load(v_cache + cache_row_offset(pt, p, n_kv_heads, kvh, v_dim) + piece * VN, vv);
+          Vec16<T>::load(v_cache + cache_row_offset(pt, p, n_kv_heads, kvh, v_row) + piece * VN, vv);
           float w = ps[j];
 #pragma unroll
           for (int e = 0; e < VN; ++e) accv[e] = fmaf(w, vv[e], accv[e]);
@@ -142,7 +146,7 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
           for (int j = 0; j < n; ++j) {
             int u = base + j;
             int p = u < n_first ? u : lo + (u - n_first);
-            const T* vrow = v_cache + cache_row_offset(pt, p, n_kv_heads, kvh, v_dim);
+            const T* vrow = v_cache + cache_row_offset(pt, p, n_kv_heads, kvh, v_row);
             a = fmaf(ps[j], to_f32<T>(vrow[d]), a);
           }
           acc[r] = a;
@@ -213,16 +217,21 @@ __global__ void attention_merge_kernel(const float* __restrict__ part, int n_spl
 // element h*v_dim.  The keys and values of the new tokens must already be in the cache.
 extern "C" int bn_attention_general_ex(const void* q, int q_stride, void* out, int out_stride, int dtype,
                                        int n_tokens, int n_heads, int n_kv_heads, int head_dim, int v_dim, float scale,
-                                       int window, int keep_first, const float* rel, int n_rel, const void* gate,
-                                       int gate_stride, const int* tok_seq, const int* tok_pos, const int* slots,
+                                       int window, int keep_first, int chunk, int v_row, const float* rel, int n_rel,
+                                       const void* gate, int gate_stride, const int* tok_seq, const int* tok_pos, const int* slots,
                                        const int* page_table, int pt_stride,
                                        const void* k_cache, const void* v_cache, float* part, int n_splits,
                                        cudaStream_t stream) {
   if (n_tokens <= 0) return BN_OK;
   if (n_splits < 1 || n_splits > 64 || (n_splits > 1 && !part)) return BN_ERR_BAD_ARG;
   if (n_splits == 1) part = nullptr;
-  if (head_dim <= 0 || head_dim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads ||
-      window < 0 || keep_first < 0 || v_dim <= 0 || v_dim > 256 || (rel && n_rel <= 0))
+  if (v_row <= 0) v_row = v_dim;
+  // value rows of whole 16-byte pieces may be up to 128 pieces wide; others are one dimension per thread, twice
+  const int vn = dtype == BN_F32 ? 4 : 8;
+  const bool wide = v_dim % vn == 0 && v_row % vn == 0 && v_dim / vn <= ATT_THREADS;
+  if (head_dim <= 0 || head_dim > 2048 || n_kv_heads <= 0 || n_heads % n_kv_heads || window < 0 || keep_first < 0 ||
+      chunk < 0 || (chunk > 0 && (window > 0 || keep_first > 0)) || v_dim <= 0 || v_row < v_dim ||
+      (!wide && v_dim > 2 * ATT_THREADS) || (rel && n_rel <= 0))
     return BN_ERR_BAD_ARG;
   if (n_heads > 65535) return BN_ERR_BAD_ARG;
   dim3 grid(n_tokens, n_heads, n_splits);
@@ -230,12 +239,12 @@ extern "C" int bn_attention_general_ex(const void* q, int q_stride, void* out, i
   if (dtype == BN_F32)
     BN_LAUNCH((attention_general_kernel<float>), grid, ATT_THREADS, smem, stream, 
         (const float*)q, q_stride, (float*)out, out_stride, n_heads, n_kv_heads, head_dim, v_dim, scale, window,
-        keep_first, rel, n_rel, (const float*)gate, gate_stride,
+        keep_first, chunk, v_row, rel, n_rel, (const float*)gate, gate_stride,
         tok_seq, tok_pos, slots, page_table, pt_stride, (const float*)k_cache, (const float*)v_cache, part, n_splits);
   else if (dtype == BN_BF16)
     BN_LAUNCH((attention_general_kernel<__nv_bfloat16>), grid, ATT_THREADS, smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, head_dim, v_dim,
-        scale, window, keep_first, rel, n_rel, (const __nv_bfloat16*)gate, gate_stride,
+        scale, window, keep_first, chunk, v_row, rel, n_rel, (const __nv_bfloat16*)gate, gate_stride,
         tok_seq, tok_pos, slots, page_table, pt_stride,
         (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, part, n_splits);
   else
@@ -259,6 +268,6 @@ extern "C" int bn_attention_general(const void* q, int q_stride, void* out, int 
                                     const int* page_table, int pt_stride,
                                     const void* k_cache, const void* v_cache, cudaStream_t stream) {
   return bn_attention_general_ex(q, q_stride, out, out_stride, dtype, n_tokens, n_heads, n_kv_heads, head_dim, head_dim,
-                                 scale, window, 0, nullptr, 0, nullptr, 0, tok_seq, tok_pos, slots, page_table,
+                                 scale, window, 0, 0, 0, nullptr, 0, nullptr, 0, tok_seq, tok_pos, slots, page_table,
                                  pt_stride, k_cache, v_cache, nullptr, 1, stream);
 }

@@ -37,7 +37,7 @@ template <int HD, bool PRECISE, int VD = HD>
 __global__ void __launch_bounds__(PF_THREADS)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
                          int out_stride, int n_heads, int n_kv_heads, int head_dim, int v_dim, float scale_log2e, int window,
-                         int keep_first, const float* __restrict__ rel, int n_rel,
+                         int keep_first, int chunk, int v_row, const float* __restrict__ rel, int n_rel,
                          const __nv_bfloat16* __restrict__ gate, int gate_stride,
                          const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
                          const int* __restrict__ seq_start, const int* __restrict__ seq_pos0,
@@ -73,7 +73,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
 
   // visible key range of this block
   const int q_first = pos0 + row0, q_last = pos0 + row0 + rows_here - 1;
-  const int lo_first = window > 0 ? max(0, q_first - window + 1) : 0;
+  // chunk > 0: a query sees the earlier keys of its own chunk of so many positions (in place of a window)
+  const int lo_first = chunk > 0 ? (q_first / chunk) * chunk : (window > 0 ? max(0, q_first - window + 1) : 0);
   const int tile_lo = lo_first / PF_N, tile_hi = q_last / PF_N;
   // with a window, keys at positions below keep_first stay visible: their tiles are walked first
   const int first_tiles = (window > 0 && keep_first > 0) ? min((keep_first + PF_N - 1) / PF_N, tile_lo) : 0;
@@ -90,7 +91,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
   auto load_kv = [&](int tile, int stage) {
     int page = pt[tile];
     const __nv_bfloat16* kb = k_cache + ((size_t)page * n_kv_heads + kvh) * BN_PAGE * head_dim;
-    const __nv_bfloat16* vb = v_cache + ((size_t)page * n_kv_heads + kvh) * BN_PAGE * v_dim;
+    const __nv_bfloat16* vb = v_cache + ((size_t)page * n_kv_heads + kvh) * BN_PAGE * v_row;  // v_row >= v_dim: the row's first v_dim numbers
     for (int p = tid; p < PF_N * CHUNKS; p += PF_THREADS) {
       int r = p / CHUNKS, c = p % CHUNKS;
       bool ok = c < real_chunks;
@@ -101,7 +102,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
       // value rows behind the sequence's last position are zero here, whatever the cache holds:
       // their weights are zero, but zero times anything must be zero
       bool okv = c < real_vchunks && tile * PF_N + r <= seq_last;
-      cp_async16(s_v + stage * VTILE_BYTES + tile_off<VD>(r, c), okv ? vb + (size_t)r * v_dim + c * 8 : vb, okv);
+      cp_async16(s_v + stage * VTILE_BYTES + tile_off<VD>(r, c), okv ? vb + (size_t)r * v_row + c * 8 : vb, okv);
     }
   };
   load_kv(tile_of(0), 0);
@@ -119,7 +120,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
   for (int e = 0; e < 2; ++e) {
     int r = warp * 16 + g + e * 8;
     qpos[e] = r < rows_here ? pos0 + row0 + r : q_first;
-    qlo[e] = window > 0 ? max(0, qpos[e] - window + 1) : 0;
+    qlo[e] = chunk > 0 ? (qpos[e] / chunk) * chunk : (window > 0 ? max(0, qpos[e] - window + 1) : 0);
   }
 
   for (int u = 0; u < n_walk; ++u) {
@@ -263,8 +264,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
 
 template <int HD, bool PRECISE = false, int VD = HD>
 static int launch_prefill(const void* q, int q_stride, void* out, int out_stride, int n_tiles, int n_heads,
-                          int n_kv_heads, int head_dim, int v_dim, float scale, int window, int keep_first, const float* rel, int n_rel,
-                          const void* gate, int gate_stride, const int* tile_seq,
+                          int n_kv_heads, int head_dim, int v_dim, float scale, int window, int keep_first, int chunk, int v_row,
+                          const float* rel, int n_rel, const void* gate, int gate_stride, const int* tile_seq,
                           const int* tile_row0, const int* seq_start, const int* seq_pos0, const int* slots,
                           const int* page_table, int pt_stride, const void* k_cache, const void* v_cache,
                           cudaStream_t stream) {
@@ -280,7 +281,7 @@ static int launch_prefill(const void* q, int q_stride, void* out, int out_stride
   dim3 grid(n_heads, n_tiles);
   BN_LAUNCH((attention_prefill_kernel<HD, PRECISE, VD>), grid, PF_THREADS, smem, stream, 
       (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, head_dim, v_dim,
-      scale * 1.4426950408889634f, window, keep_first, rel, n_rel, (const __nv_bfloat16*)gate, gate_stride, tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table, pt_stride,
+      scale * 1.4426950408889634f, window, keep_first, chunk, v_row, rel, n_rel, (const __nv_bfloat16*)gate, gate_stride, tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table, pt_stride,
       (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache);
   BN_CHECK_LAUNCH();
   return BN_OK;
@@ -292,19 +293,23 @@ static int launch_prefill(const void* q, int q_stride, void* out, int out_stride
 // Optional (0 / null: off): with a window, keys below position keep_first stay visible; rel
 // [n_rel, n_heads] float32 is added to the scaled scores by distance (the last row for every longer
 // one); gate [tokens, gate_stride] holds per token and head a number whose logistic function
-// multiplies the head's output.
+// multiplies the head's output; chunk: positions are cut into chunks of so many and a query sees the
+// earlier keys of its own chunk (in place of a window); v_row: the width of a row of the value
+// plane when the values are the first v_dim numbers of wider rows (0: v_dim).
 extern "C" int bn_attention_prefill_ex(const void* q, int q_stride, void* out, int out_stride, int n_tiles, int n_heads,
                                        int n_kv_heads, int head_dim, int v_dim, float scale, int window, int keep_first,
-                                       const float* rel, int n_rel, const void* gate, int gate_stride, int precise,
+                                       int chunk, int v_row, const float* rel, int n_rel, const void* gate, int gate_stride, int precise,
                                        const int* tile_seq, const int* tile_row0, const int* seq_start,
                                        const int* seq_pos0, const int* slots, const int* page_table, int pt_stride,
                                        const void* k_cache, const void* v_cache, cudaStream_t stream) {
   if (n_tiles <= 0) return BN_OK;
+  if (v_row <= 0) v_row = v_dim;
+  if (chunk < 0 || (chunk > 0 && (window > 0 || keep_first > 0)) || v_row < v_dim || v_row % 8) return BN_ERR_BAD_ARG;
   if (head_dim <= 0 || head_dim % 16 || head_dim > 256 || n_kv_heads <= 0 || n_heads % n_kv_heads || window < 0 ||
       n_heads > 65535 || (q_stride % 8) || (out_stride % 2) || (((uintptr_t)q) & 15) || keep_first < 0 ||
       (rel && n_rel <= 0) || v_dim <= 0 || v_dim % 16 || v_dim > 256 || (v_dim != head_dim && !precise))
     return BN_ERR_BAD_ARG;
-#define BN_PF_ARGS q, q_stride, out, out_stride, n_tiles, n_heads, n_kv_heads, head_dim, v_dim, scale, window, keep_first, rel, \
+#define BN_PF_ARGS q, q_stride, out, out_stride, n_tiles, n_heads, n_kv_heads, head_dim, v_dim, scale, window, keep_first, chunk, v_row, rel, \
                    n_rel, gate, gate_stride, tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table, pt_stride,      \
                    k_cache, v_cache, stream
   if (precise) {
@@ -332,6 +337,6 @@ extern "C" int bn_attention_prefill(const void* q, int q_stride, void* out, int 
                                     const int* slots, const int* page_table, int pt_stride, const void* k_cache,
                                     const void* v_cache, cudaStream_t stream) {
   return bn_attention_prefill_ex(q, q_stride, out, out_stride, n_tiles, n_heads, n_kv_heads, head_dim, head_dim, scale, window, 0,
-                                 nullptr, 0, nullptr, 0, 0, tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table,
+                                 0, 0, nullptr, 0, nullptr, 0, 0, tile_seq, tile_row0, seq_start, seq_pos0, slots, page_table,
                                  pt_stride, k_cache, v_cache, stream);
 }

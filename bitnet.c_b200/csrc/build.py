@@ -47,6 +47,8 @@ SOURCES: Dict[str, str] = {
     "unit_norm": "unit_norm.cu",
     "mlstm": "mlstm.cu",
     "moe": "moe.cu",
+    "rotary_pairs": "rotary_pairs.cu",
+    "delta_rule": "delta_rule.cu",
 }
 
 NVCC_FLAGS = [

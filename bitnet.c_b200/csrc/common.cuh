@@ -107,6 +107,16 @@ __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// The activation of a gated feed-forward, by code: 0 SiLU, g / (1 + e^-g); 1 the tanh form of GELU,
+// 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).  Products with a gated epilogue take the code in
+// the bits above the low byte of their `mode` argument (mode 2 | BN_ACT_GELU_TANH << 8).
+#define BN_ACT_SILU 0
+#define BN_ACT_GELU_TANH 1
+__device__ __forceinline__ float glu_activation(float g, int act) {
+  if (act == BN_ACT_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.0f + expf(-g));
+}
+
 // Load/store of one element of a buffer whose type is only known by code.
 __device__ __forceinline__ float load_as_f32(const void* p, int dtype, size_t i) {
   return dtype == BN_F32 ? ((const float*)p)[i] : __bfloat162float(((const __nv_bfloat16*)p)[i]);

@@ -41,6 +41,7 @@ struct GmArgs {
   void* out;        // modes 0, 2: [M, ldo]
   int out_dtype;
   int M, N, K, ldo, mode;
+  int act;          // mode 2: the gate's activation (BN_ACT_*)
   int k_blocks, m_tiles, n_tiles;
   const float* row_ss;  // [ss_parts][ss_stride]: sums of squares of the input rows, or null (rows are plain)
   int ss_parts, ss_stride;
@@ -54,7 +55,7 @@ struct GmArgs {
   int* status;
 };
 
-__device__ __forceinline__ float gm_silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+__device__ __forceinline__ float gm_glu_mul(float g, float u, int act) { return glu_activation(g, act) * u; }
 
 // The epilogue of one tile for one thread in modes 0 and 2: row m of the output, the 256 columns
 // from n0 on, read from the thread's TMEM lane at acc_addr (see the modes at the top of this file).
@@ -89,7 +90,7 @@ __device__ __forceinline__ void gm_finish_tile(const GmArgs& a, unsigned acc_add
         if (n0 + c + g * 16 >= a.N) continue;  // N is a multiple of 16 here
         float r[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) r[e] = gm_silu_mul(v[g * 16 + e] * scale, v[g * 16 + 8 + e] * scale);
+        for (int e = 0; e < 8; ++e) r[e] = gm_glu_mul(v[g * 16 + e] * scale, v[g * 16 + 8 + e] * scale, a.act);
         const size_t oc = (size_t)m * a.ldo + (size_t)((n0 + c) >> 1) + g * 8;
         if (a.out_dtype == BN_BF16) {
           *reinterpret_cast<uint4*>((__nv_bfloat16*)a.out + oc) =
@@ -547,6 +548,9 @@ extern "C" int bn_gemm_tc(const void* x, const void* w, int M, int N, int K, voi
                           const void* gain, int gain_dtype, void* xg, float* ss_out, int ss_out_stride, int* status,
                           cudaStream_t stream) {
   if (M <= 0 || N <= 0) return BN_OK;
+  const int act = mode >> 8;
+  mode &= 255;
+  if (act != BN_ACT_SILU && act != BN_ACT_GELU_TANH) return BN_ERR_BAD_ARG;
   if (K <= 0 || K % 8 || N % 8 || !status || (((uintptr_t)x | (uintptr_t)w) & 15)) return BN_ERR_BAD_ARG;
   if (mode == 0 || mode == 2) {
     if (!out || (out_dtype != BN_BF16 && out_dtype != BN_F32) || ((uintptr_t)out & 15)) return BN_ERR_BAD_ARG;
@@ -566,7 +570,7 @@ extern "C" int bn_gemm_tc(const void* x, const void* w, int M, int N, int K, voi
       !tma_map_bf16_rows(&mw, w, (unsigned long long)N, (unsigned long long)K, pairs ? GM_BN / 2 : GM_BN))
     return BN_ERR_BAD_ARG;
   GmArgs a = {};
-  a.out = out; a.out_dtype = out_dtype; a.M = M; a.N = N; a.K = K; a.ldo = ldo; a.mode = mode;
+  a.out = out; a.out_dtype = out_dtype; a.M = M; a.N = N; a.K = K; a.ldo = ldo; a.mode = mode; a.act = act;
   a.k_blocks = (K + GM_BK - 1) / GM_BK; a.m_tiles = (M + GM_BM - 1) / GM_BM; a.n_tiles = (N + GM_BN - 1) / GM_BN;
   a.row_ss = row_ss; a.ss_parts = ss_parts; a.ss_stride = ss_stride; a.inv_width = inv_width; a.eps = eps;
   a.residual = residual; a.gain = gain; a.gain_dtype = gain_dtype; a.xg = (__nv_bfloat16*)xg; a.ss_out = ss_out;

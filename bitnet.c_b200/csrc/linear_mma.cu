@@ -45,6 +45,7 @@ struct LmArgs {
   int M, N, K;
   int k_per_split;  // multiple of LM_KC
   int mode;         // 0 store, 1 partial, 2 swiglu
+  int act;          // mode 2: the gate's activation (BN_ACT_*)
   int ldo;
   float* scratch;   // modes 0/2 with gridDim.y > 1: [splits][row blocks][64 rows][8*NT] partial tiles
   int* counters;    // one ticket counter per row block, zero before and after the launch
@@ -186,7 +187,7 @@ __global__ void __launch_bounds__(128) linear_mma_kernel(LmArgs a) {
         // rows [16j, 16j+8) are gate rows 8j.., rows [16j+8, 16j+16) the matching up rows
         int i = (row0 >> 4) * 8 + g;
         if (n_hi < a.N) {
-          float s = v_lo / (1.0f + expf(-v_lo));
+          float s = glu_activation(v_lo, a.act);
           store_from_f32(a.out, a.out_dtype, (size_t)m * a.ldo + i, s * v_hi);
         }
       }
@@ -204,12 +205,15 @@ extern "C" int bn_linear_mma(const void* x, const void* w, void* out, int out_dt
                              int mode, int n_splits, float* scratch, long long scratch_floats, int* counters,
                              int n_counters, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return BN_OK;
+  const int act = mode >> 8;
+  mode &= 255;
+  if (act != BN_ACT_SILU && act != BN_ACT_GELU_TANH) return BN_ERR_BAD_ARG;
   if (M > 64 || K <= 0 || K % 8 || n_splits < 1 || mode < 0 || mode > 2) return BN_ERR_BAD_ARG;
   if (mode == 2 && (N % 16)) return BN_ERR_BAD_ARG;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return BN_ERR_BAD_ARG;
   LmArgs a;
   a.x = (const __nv_bfloat16*)x; a.w = (const __nv_bfloat16*)w; a.out = out; a.out_dtype = out_dtype;
-  a.M = M; a.N = N; a.K = K; a.mode = mode; a.ldo = ldo; a.scratch = scratch; a.counters = counters;
+  a.M = M; a.N = N; a.K = K; a.mode = mode; a.act = act; a.ldo = ldo; a.scratch = scratch; a.counters = counters;
   int chunks = (K + LM_KC - 1) / LM_KC;
   if (n_splits > chunks) n_splits = chunks;
   a.k_per_split = ((chunks + n_splits - 1) / n_splits) * LM_KC;

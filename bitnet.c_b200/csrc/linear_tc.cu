@@ -73,6 +73,7 @@ struct TcArgs {
   int M, N, K;
   int ldo;
   int mode;        // 0 store, 2 swiglu, 3 residual add + gain + sums of squares
+  int act;         // mode 2: the gate's activation (BN_ACT_*)
   int k_blocks;    // ceil(K / 64)
   const float* row_ss;   // [ss_parts][ss_stride]: sums of squares of the input rows, or null (rows are plain)
   int ss_parts, ss_stride;
@@ -461,7 +462,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             if (m < a.M) {
               const float rs = a.row_ss != nullptr ? row_scale[m] : 1.0f;
               const float gv = g[i] * rs, uv = u[i] * rs;
-              store_from_f32(a.out, a.out_dtype, (size_t)m * a.ldo + col, __fdividef(gv, 1.0f + __expf(-gv)) * uv);
+              store_from_f32(a.out, a.out_dtype, (size_t)m * a.ldo + col,
+                             (a.act == BN_ACT_SILU ? __fdividef(gv, 1.0f + __expf(-gv)) : glu_activation(gv, a.act)) * uv);
             }
           }
         }
@@ -585,6 +587,9 @@ extern "C" int bn_linear_tc_ex(const void* x, const void* w, void* out, int out_
                                float eps, const void* gain, int gain_dtype, void* xg, float* ss_out, int ss_out_stride,
                                int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return BN_OK;
+  const int act = mode >> 8;
+  mode &= 255;
+  if (act != BN_ACT_SILU && act != BN_ACT_GELU_TANH) return BN_ERR_BAD_ARG;
   if (M > 64 || K <= 0 || K % 8 || cluster < 0 || cluster > 8 || (mode != 0 && mode != 2 && mode != 3) || !status)
     return BN_ERR_BAD_ARG;
   if (mode == 2 && (N % 16)) return BN_ERR_BAD_ARG;
@@ -614,7 +619,7 @@ extern "C" int bn_linear_tc_ex(const void* x, const void* w, void* out, int out_
   CUtensorMap mw, mx;
   if (!tma_map_bf16_rows(&mw, w, N, K, TC_BM) || !tma_map_bf16_rows(&mx, x, M, K, mp)) return BN_ERR_BAD_ARG;
   TcArgs a;
-  a.out = out; a.out_dtype = out_dtype; a.M = M; a.N = N; a.K = K; a.ldo = ldo; a.mode = mode;
+  a.out = out; a.out_dtype = out_dtype; a.M = M; a.N = N; a.K = K; a.ldo = ldo; a.mode = mode; a.act = act;
   a.k_blocks = k_blocks; a.status = status;
   a.row_ss = row_ss; a.ss_parts = ss_parts; a.ss_stride = ss_stride; a.inv_width = inv_width; a.eps = eps;
   a.gain = gain; a.gain_dtype = gain_dtype; a.xg = (__nv_bfloat16*)xg; a.ss_out = ss_out; a.ss_out_stride = ss_out_stride;
@@ -628,7 +633,7 @@ extern "C" int bn_linear_tc_ex(const void* x, const void* w, void* out, int out_
 // The plain forms (modes 0 and 2, plain input rows).
 extern "C" int bn_linear_tc(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int ldo,
                             int mode, int cluster, int* status, cudaStream_t stream) {
-  if (mode == 3) return BN_ERR_BAD_ARG;
+  if ((mode & 255) == 3) return BN_ERR_BAD_ARG;
   return bn_linear_tc_ex(x, w, out, out_dtype, M, N, K, ldo, mode, cluster, nullptr, 0, 0, 0.f, 0.f, nullptr, 0, nullptr,
                          nullptr, 0, status, stream);
 }

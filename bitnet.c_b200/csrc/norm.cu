@@ -256,3 +256,136 @@ extern "C" int bn_scaled_add_rmsnorm(float* x, float alpha, const void* delta, i
   BN_CHECK_LAUNCH();
   return BN_OK;
 }
+
+// ---- parallel blocks ---------------------------------------------------------------------------
+// x += a (+ b): the deltas of the two sublayers of a parallel block (any element type) meet in the
+// float32 residual; `cast` (optional) receives the new rows in the compute type for the product
+// that reads them next.
+__global__ void residual_add_kernel(float* __restrict__ x, const void* __restrict__ a, int a_dtype,
+                                    const void* __restrict__ b, int b_dtype, void* __restrict__ cast, int cast_dtype,
+                                    size_t total, int vec4) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * (vec4 ? 4 : 1);
+  if (i >= total) return;
+  if (vec4) {
+    float4 v = *reinterpret_cast<const float4*>(x + i);
+    float4 d = load4_as_f32(a, a_dtype, i);
+    if (b) {
+      float4 e = load4_as_f32(b, b_dtype, i);
+      d.x += e.x; d.y += e.y; d.z += e.z; d.w += e.w;  // the sublayers' sum first, then onto the stream
+    }
+    v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+    *reinterpret_cast<float4*>(x + i) = v;
+    if (cast) store4_from_f32(cast, cast_dtype, i, v);
+  } else {
+    float d = load_as_f32(a, a_dtype, i);
+    if (b) d += load_as_f32(b, b_dtype, i);
+    float v = x[i] + d;
+    x[i] = v;
+    if (cast) store_from_f32(cast, cast_dtype, i, v);
+  }
+}
+
+extern "C" int bn_residual_add(float* x, const void* a, int a_dtype, const void* b, int b_dtype, void* cast, int cast_dtype,
+                               long long total, cudaStream_t stream) {
+  if (total <= 0) return BN_OK;
+  if (!x || !a) return BN_ERR_BAD_ARG;
+  int vec4 = total % 4 == 0 && (((uintptr_t)x | (uintptr_t)a | (uintptr_t)b | (uintptr_t)cast) & 15) == 0;
+  size_t threads = vec4 ? (size_t)total / 4 : (size_t)total;
+  BN_LAUNCH(residual_add_kernel, (unsigned)((threads + 255) / 256), 256, 0, stream, x, a, a_dtype, b, b_dtype, cast,
+            cast_dtype, (size_t)total, vec4);
+  return BN_OK;
+}
+
+// x += y / sqrt(mean(y^2) + eps_y) * wy: a delta that enters the stream through a norm of its own.
+// Then, if `w` is given, out[r] = x * rsqrt(mean(x^2) + eps) * w: the norm that reads the stream next,
+// in the same pass (out in the compute type).  One block per row; float32 statistics.
+__global__ void add_normed_kernel(float* __restrict__ x, const void* __restrict__ y, int y_dtype,
+                                  const void* __restrict__ wy, int wy_dtype, float eps_y, const void* __restrict__ w,
+                                  int w_dtype, float eps, void* __restrict__ out, int out_dtype, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float v[];  // width floats, then 32 for the reductions
+  float* scratch = v + width;
+  const size_t row = blockIdx.x;
+  float* xr = x + row * width;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float a = load_as_f32(y, y_dtype, row * width + i);
+    v[i] = a;
+    ss += a * a;
+  }
+  ss = block_sum(ss, scratch);
+  const float scale_y = 1.0f / sqrtf(ss / (float)width + eps_y);
+  float sx = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float a = xr[i] + v[i] * scale_y * load_as_f32(wy, wy_dtype, i);
+    xr[i] = a;
+    v[i] = a;
+    sx += a * a;
+  }
+  if (!w) return;
+  sx = block_sum(sx, scratch);
+  const float scale = 1.0f / sqrtf(sx / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    store_from_f32(out, out_dtype, row * width + i, v[i] * scale * load_as_f32(w, w_dtype, i));
+}
+
+extern "C" int bn_add_normed(float* x, const void* y, int y_dtype, const void* wy, int wy_dtype, float eps_y, const void* w,
+                             int w_dtype, float eps, void* out, int out_dtype, int n_rows, int width, cudaStream_t stream) {
+  if (n_rows <= 0) return BN_OK;
+  if (width <= 0 || !(eps_y > 0.f) || !x || !y || !wy || (w && (!out || !(eps > 0.f)))) return BN_ERR_BAD_ARG;
+  size_t smem = ((size_t)width + 32) * sizeof(float);
+  if (smem > 200 * 1024) return BN_ERR_BAD_ARG;
+  if (smem > 48 * 1024) {
+    static size_t granted = 0;
+    if (smem > granted) {
+      cudaError_t e = cudaFuncSetAttribute(add_normed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;
+      granted = smem;
+    }
+  }
+  int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  BN_LAUNCH(add_normed_kernel, n_rows, threads, smem, stream, x, y, y_dtype, wy, wy_dtype, eps_y, w, w_dtype, eps, out,
+            out_dtype, width);
+  return BN_OK;
+}
+
+// RMS norms of up to two slices of every row, in place: x[t, off_s : off_s + len_s] becomes
+// v * rsqrt(mean(v^2) + eps) * w_s (the latents of a low-rank projection, each with its own gain).
+// One warp per (row, slice); float32 statistics; x and the gains of type `dtype` / `w_dtype`.
+__global__ void rmsnorm_slices_kernel(void* __restrict__ x, int dtype, int stride, int n_rows, int off0, int len0,
+                                      const void* __restrict__ w0, int off1, int len1, const void* __restrict__ w1,
+                                      int w_dtype, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n_slices = len1 > 0 ? 2 : 1;
+  const int item = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (item >= n_rows * n_slices) return;
+  const int row = item / n_slices, s = item - row * n_slices;
+  const int off = s ? off1 : off0, len = s ? len1 : len0;
+  const void* w = s ? w1 : w0;
+  const size_t base = (size_t)row * stride + off;
+  float ss = 0.f;
+  for (int i = lane; i < len; i += 32) {
+    float a = load_as_f32(x, dtype, base + i);
+    ss += a * a;
+  }
+  ss = warp_sum(ss);
+  const float scale = 1.0f / sqrtf(ss / (float)len + eps);
+  for (int i = lane; i < len; i += 32)
+    store_from_f32(x, dtype, base + i, load_as_f32(x, dtype, base + i) * scale * load_as_f32(w, w_dtype, i));
+}
+
+extern "C" int bn_rmsnorm_slices(void* x, int dtype, int stride, int n_rows, int off0, int len0, const void* w0, int off1,
+                                 int len1, const void* w1, int w_dtype, float eps, cudaStream_t stream) {
+  if (n_rows <= 0) return BN_OK;
+  if (!x || !w0 || len0 <= 0 || off0 < 0 || off0 + len0 > stride || !(eps > 0.f) ||
+      (len1 > 0 && (!w1 || off1 < 0 || off1 + len1 > stride)) || len1 < 0)
+    return BN_ERR_BAD_ARG;
+  const int items = n_rows * (len1 > 0 ? 2 : 1);
+  BN_LAUNCH(rmsnorm_slices_kernel, (unsigned)((items + 7) / 8), 256, 0, stream, x, dtype, stride, n_rows, off0, len0, w0, off1,
+            len1, w1, w_dtype, eps);
+  return BN_OK;
+}

@@ -199,6 +199,35 @@ def silu_mul(h: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def glu_mul(h: torch.Tensor, out: torch.Tensor, act: int = 0) -> torch.Tensor:
+    """``silu_mul`` with the gate's activation by code (ACT_SILU, ACT_GELU_TANH)."""
+    _need(h, "h", dims=2)
+    _need(out, "out", h.dtype, 2)
+    inter = h.shape[1] // 2
+    if h.shape[1] != 2 * inter or out.shape != (h.shape[0], inter):
+        raise KernelError(f"glu_mul: h {tuple(h.shape)} and out {tuple(out.shape)} do not fit")
+    _check(_fn("act", "bn_glu_mul")(_ptr(h), _ptr(out), int(_code(h)), int(h.shape[0]), int(inter), int(act), _stream()),
+           "glu_mul")
+    return out
+
+
+def gated_lookup(pre: torch.Tensor, table: torch.Tensor, col0: int, tokens: torch.Tensor, dim: int, act: int = 0) -> torch.Tensor:
+    """out[t, j] = act(pre[t, j]) * table[tokens[t], col0 + j] for j < dim (an id outside the table gives zeros);
+    ``pre`` may be a view into wider rows; the result has ``pre``'s type."""
+    if not pre.is_cuda or pre.dim() != 2 or pre.stride(1) != 1 or pre.shape[1] < dim:
+        raise KernelError("gated_lookup: pre must be a CUDA matrix with unit inner stride and at least dim columns")
+    _need(table, "table", dims=2)
+    _need(tokens, "tokens", torch.int32, 1)
+    n = tokens.shape[0]
+    if pre.shape[0] < n or col0 < 0 or col0 + dim > table.shape[1]:
+        raise KernelError("gated_lookup: sizes do not fit")
+    out = torch.empty((n, dim), dtype=pre.dtype, device=pre.device)
+    _check(_fn("act", "bn_gated_lookup")(_ptr(pre), int(pre.stride(0)), int(_code(pre)), _ptr(table), int(_code(table)),
+                                         int(table.shape[1]), int(col0), int(table.shape[0]), _ptr(tokens), _ptr(out), int(n),
+                                         int(dim), int(act), _stream()), "gated_lookup")
+    return out
+
+
 def glu_limited(h: torch.Tensor, out: torch.Tensor, limit: float, slope: float) -> torch.Tensor:
     """Rows of h hold ``inter`` gate values and then ``inter`` up values: g = min(gate, limit),
     u = clamp(up, -limit, limit), out = g * sigmoid(slope * g) * (u + 1)."""
@@ -290,7 +319,7 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
                       tok_pos: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
                       k_cache: torch.Tensor, v_cache: torch.Tensor, *, keep_first: int = 0,
                       rel: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-                      gate_stride: int = 0, max_keys: int = 0) -> torch.Tensor:
+                      gate_stride: int = 0, max_keys: int = 0, chunk: int = 0, v_dim: int = 0) -> torch.Tensor:
     """Causal attention of every new token over its sequence's pages; q may be a view into a wider row.
     ``max_keys`` (optional): a bound on the keys any of the tokens sees; with few tokens and many keys the
     keys of a token are then shared out over several blocks whose results a second kernel merges.
@@ -299,21 +328,34 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
     window, keys at positions below ``keep_first`` stay visible.  ``rel`` ``[distances, n_heads]``
     float32 is added to the scaled scores by distance (the last row serves every longer distance).
     ``gate`` (a view with unit inner stride, row stride ``gate_stride``) holds one number per token and
-    head whose logistic function multiplies the head's output."""
+    head whose logistic function multiplies the head's output.  ``chunk`` > 0 (in place of a window):
+    positions are cut into chunks of so many and a token sees the earlier keys of its own chunk.
+    ``v_cache`` None with ``v_dim``: the values are the first ``v_dim`` numbers of the key rows."""
     if not q.is_cuda or q.stride(-1) != 1:
         raise KernelError("attention: q must be a CUDA tensor with unit inner stride")
+    v_row = 0
+    if v_cache is None:
+        if not 0 < v_dim <= head_dim:
+            raise KernelError("attention: values inside the key rows need 0 < v_dim <= head_dim")
+        v_cache, v_row, inner = k_cache, head_dim, v_dim
+    else:
+        inner = v_cache.shape[3]
     _need(out, "out", q.dtype, 2)
     for t, nm in ((tok_seq, "tok_seq"), (tok_pos, "tok_pos"), (slots, "slots")):
         _need(t, nm, torch.int32, 1)
     _need(page_table, "page_table", torch.int32, 2)
     _need(k_cache, "k_cache", q.dtype, 4)
     _need(v_cache, "v_cache", q.dtype, 4)
-    v_dim = v_cache.shape[3]
+    v_dim = inner
     if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or tuple(k_cache.shape[:3]) != tuple(v_cache.shape[:3]):
         raise KernelError(f"attention: cache {tuple(k_cache.shape)} / {tuple(v_cache.shape)} is not "
                           f"[pages, {n_kv_heads}, {PAGE}, {head_dim} / value width]")
-    if not 0 < head_dim <= 256 or v_dim > 256:
-        raise KernelError(f"attention: head_dim={head_dim} and the value width {v_dim} must be at most 256")
+    piece = 4 if q.dtype == torch.float32 else 8
+    if not 0 < head_dim <= 2048 or (v_dim > 256 and (v_dim % piece or (v_row or v_dim) % piece or v_dim // piece > 128)):
+        raise KernelError(f"attention: head_dim={head_dim} (at most 2048) or the value width {v_dim} (at most 256, or whole "
+                          f"16-byte pieces up to 128 of them) is not supported")
+    if chunk < 0 or (chunk > 0 and (window > 0 or keep_first > 0)):
+        raise KernelError("attention: chunks take the place of a window")
     if n_heads % n_kv_heads:
         raise KernelError(f"attention: {n_heads} heads are not a multiple of {n_kv_heads} key/value heads")
     if out.shape[0] < n_tokens or out.shape[1] != n_heads * v_dim:
@@ -330,7 +372,7 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
     splits = 1
     if max_keys > 2 * DECODE_CHUNK and n_tokens * n_heads < 2 * n_sms(q.device):
         splits = min(16, (max_keys + DECODE_CHUNK - 1) // DECODE_CHUNK, max(1, 4 * n_sms(q.device) // (n_tokens * n_heads)))
-    if (keep_first or rel is not None or gate is not None or v_dim != head_dim or splits > 1):
+    if (keep_first or rel is not None or gate is not None or v_dim != head_dim or splits > 1 or chunk or v_row):
         part = None
         if splits > 1:
             part = torch.empty(n_tokens * n_heads * splits * (v_dim + 2), dtype=torch.float32, device=q.device)
@@ -338,8 +380,8 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
             LAUNCHES += 1  # the kernel that merges the splits
         _check(_fn("attention", "bn_attention_general_ex")(
             _ptr(q), int(q_stride), _ptr(out), int(out.shape[1]), int(_code(q)), int(n_tokens), int(n_heads),
-            int(n_kv_heads), int(head_dim), int(v_dim), c_float(scale), int(window), int(keep_first), _ptr(rel), int(n_rel),
-            _ptr(gate), int(gate_stride), _ptr(tok_seq), _ptr(tok_pos), _ptr(slots), _ptr(page_table),
+            int(n_kv_heads), int(head_dim), int(v_dim), c_float(scale), int(window), int(keep_first), int(chunk), int(v_row),
+            _ptr(rel), int(n_rel), _ptr(gate), int(gate_stride), _ptr(tok_seq), _ptr(tok_pos), _ptr(slots), _ptr(page_table),
             int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), _ptr(part), int(splits), _stream()), "attention_general")
         return out
     _check(_fn("attention", "bn_attention_general")(
@@ -355,13 +397,21 @@ def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_heads
                       seq_start: torch.Tensor, seq_pos0: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
                       k_cache: torch.Tensor, v_cache: torch.Tensor, *, keep_first: int = 0,
                       rel: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, gate_stride: int = 0,
-                      precise: bool = False) -> torch.Tensor:
+                      precise: bool = False, chunk: int = 0, v_dim: int = 0) -> torch.Tensor:
     """bfloat16 causal attention of runs of new tokens on the tensor cores; block i handles up to 64
     new tokens of sequence tile_seq[i] from its row tile_row0[i] on.  ``keep_first``, ``rel`` and ``gate`` as
     for ``attention_general``; a value head may have a width of its own (``v_cache``'s rows; with ``precise``); ``precise``: the softmax weights enter the second product with 16 bits of
-    mantissa (as two bfloat16 terms) instead of 8."""
+    mantissa (as two bfloat16 terms) instead of 8.  ``chunk`` and ``v_cache`` None with ``v_dim`` as for
+    ``attention_general``."""
     if not q.is_cuda or q.stride(-1) != 1 or q.dtype != torch.bfloat16:
         raise KernelError("attention_prefill: q must be a bfloat16 CUDA tensor with unit inner stride")
+    v_row = 0
+    if v_cache is None:
+        if not 0 < v_dim <= head_dim:
+            raise KernelError("attention_prefill: values inside the key rows need 0 < v_dim <= head_dim")
+        v_cache, v_row, inner = k_cache, head_dim, v_dim
+    else:
+        inner = v_cache.shape[3]
     _need(out, "out", torch.bfloat16, 2)
     for t, nm in ((tile_seq, "tile_seq"), (tile_row0, "tile_row0"), (seq_start, "seq_start"), (seq_pos0, "seq_pos0"),
                   (slots, "slots")):
@@ -369,7 +419,7 @@ def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_heads
     _need(page_table, "page_table", torch.int32, 2)
     _need(k_cache, "k_cache", torch.bfloat16, 4)
     _need(v_cache, "v_cache", torch.bfloat16, 4)
-    v_dim = v_cache.shape[3]
+    v_dim = inner
     if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or tuple(k_cache.shape[:3]) != tuple(v_cache.shape[:3]):
         raise KernelError(f"attention_prefill: cache {tuple(k_cache.shape)} / {tuple(v_cache.shape)} is not "
                           f"[pages, {n_kv_heads}, {PAGE}, {head_dim} / value width]")
@@ -388,10 +438,11 @@ def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_heads
     if gate is not None and (not gate.is_cuda or gate.dtype != torch.bfloat16 or gate.stride(-1) != 1
                              or gate.shape[-1] < n_heads or gate_stride <= 0):
         raise KernelError("attention_prefill: gate must be a bfloat16 CUDA view with unit inner stride and one number per head")
-    if keep_first or rel is not None or gate is not None or precise:
+    if keep_first or rel is not None or gate is not None or precise or chunk or v_row:
         _check(_fn("attention_prefill", "bn_attention_prefill_ex")(
             _ptr(q), int(q_stride), _ptr(out), int(out.shape[1]), int(tile_seq.shape[0]), int(n_heads),
-            int(n_kv_heads), int(head_dim), int(v_dim), c_float(scale), int(window), int(keep_first), _ptr(rel), int(n_rel), _ptr(gate),
+            int(n_kv_heads), int(head_dim), int(v_dim), c_float(scale), int(window), int(keep_first), int(chunk), int(v_row),
+            _ptr(rel), int(n_rel), _ptr(gate),
             int(gate_stride), int(bool(precise)), _ptr(tile_seq), _ptr(tile_row0), _ptr(seq_start), _ptr(seq_pos0), _ptr(slots),
             _ptr(page_table), int(page_table.shape[1]), _ptr(k_cache), _ptr(v_cache), _stream()), "attention_prefill")
         return out
@@ -750,8 +801,12 @@ USE_FUSED_NORM = True  # products of few rows add to the residual and prepare th
 # (tests and comparisons set it to False)
 
 
+ACT_SILU, ACT_GELU_TANH = 0, 1  # the gate's activation in a gated product (BN_ACT_* in common.cuh)
+ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH}
+
+
 def linear_tc(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: bool = False,
-              cluster: int = 0, sink: Optional[NormSink] = None, _checked: bool = False):
+              cluster: int = 0, sink: Optional[NormSink] = None, _checked: bool = False, act: int = 0):
     """x[M, K] . w[N, K]^T for M <= 64 in bfloat16 on tcgen05 tensor cores with TMA-fed operands.
     ``cluster`` blocks (1 to 8) share the inner dimension of each 128-row tile of w and add their
     parts up through distributed shared memory (0: chosen from the number of tiles).  ``x`` may be
@@ -798,7 +853,7 @@ def linear_tc(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swigl
     cols = N // 2 if swiglu else N
     out = torch.empty((M, cols), dtype=out_dtype, device=dev)
     _check(fn(c_void_p(x.data_ptr()), c_void_p(w.data_ptr()), c_void_p(out.data_ptr()), _DT[out_dtype], M, N, K, cols,
-              2 if swiglu else 0, cluster, *row, _NULL, 0, _NULL, _NULL, 0, _tc_status_arg(dev), _stream()), "linear_tc")
+              (2 | act << 8) if swiglu else 0, cluster, *row, _NULL, 0, _NULL, _NULL, 0, _tc_status_arg(dev), _stream()), "linear_tc")
     return out
 
 
@@ -836,7 +891,7 @@ def own_gemm_sink_rows(rows: int) -> bool:
 
 
 def gemm_tc(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: bool = False,
-            sink: Optional[NormSink] = None):
+            sink: Optional[NormSink] = None, act: int = 0):
     """x[M, K] . w[N, K]^T for many rows in bfloat16 on tcgen05 tensor cores (gemm_tc.cu).  ``x`` may be
     ``RowScaled``; ``swiglu`` and ``sink`` as for ``linear`` (the activation, or the residual add with
     the next norm's gain and sums of squares, happen in the product's epilogue)."""
@@ -878,7 +933,7 @@ def gemm_tc(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu:
     cols = N // 2 if swiglu else N
     out = torch.empty((M, cols), dtype=out_dtype, device=x.device)
     _check(fn(_ptr(x), _ptr(w), int(M), int(N), int(K), _ptr(out), int(_DT[out_dtype]), int(cols),
-              int(2 if swiglu else 0), *row, c_void_p(None), c_void_p(None), int(0), c_void_p(None), c_void_p(None),
+              int((2 | act << 8) if swiglu else 0), *row, c_void_p(None), c_void_p(None), int(0), c_void_p(None), c_void_p(None),
               int(0), status, _stream()), "gemm_tc")
     return out
 
@@ -910,7 +965,7 @@ def _own_gemm_fits(x, w: torch.Tensor, swiglu: bool, out_dtype, kind: str) -> bo
 
 
 def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: bool = False,
-           partial_sums: bool = False, sink: Optional[NormSink] = None):
+           partial_sums: bool = False, sink: Optional[NormSink] = None, act: int = 0):
     """x[M, K] . w[N, K]^T.  A weight kept in float32 makes the product float32 whatever x is.
 
     ``x`` may be ``RowScaled`` (the output of a norm that a product's epilogue prepared).  With
@@ -919,7 +974,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: 
     else a tensor from the norm kernel.
 
     ``swiglu``: w holds gate and up rows in alternating blocks of 8 and the result is
-    silu(gate) * up, ``[M, N / 2]``.  ``partial_sums``: return the float32 partial sums
+    act(gate) * up, ``[M, N / 2]`` (``act``: ACT_SILU or ACT_GELU_TANH).  ``partial_sums``: return the float32 partial sums
     ``[parts, M, N]`` of a product that split its inner dimension instead of their sum
     (``add_rmsnorm`` can add them up); by default the product sums them itself.
     """
@@ -938,23 +993,23 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: 
         if (not swiglu and not isinstance(x, RowScaled) and tuple(sink.residual.shape) == (M, N)
                 and _own_gemm_fits(x, w, False, None, "sink") and not partial_sums):
             return gemm_tc(x, w, sink=sink)
-        delta = linear(x, w, out_dtype=out_dtype, swiglu=swiglu)
+        delta = linear(x, w, out_dtype=out_dtype, swiglu=swiglu, act=act)
         normed = torch.empty((M, sink.residual.shape[1]), dtype=delta.dtype, device=delta.device)
         return add_rmsnorm(sink.residual, delta, sink.weight, sink.eps, normed)
     if isinstance(x, RowScaled):
         if fast:
-            return linear_tc(x, w, out_dtype=out_dtype or x.dtype, swiglu=swiglu, _checked=True)
+            return linear_tc(x, w, out_dtype=out_dtype or x.dtype, swiglu=swiglu, _checked=True, act=act)
         if _own_gemm_fits(x.x, w, swiglu, out_dtype, "scaled") and not partial_sums:
-            return gemm_tc(x, w, out_dtype=out_dtype or x.dtype, swiglu=swiglu)
+            return gemm_tc(x, w, out_dtype=out_dtype or x.dtype, swiglu=swiglu, act=act)
         x = x.dense()
     _need(x, "x", dims=2)
     out_dtype = out_dtype or x.dtype
     if x.dtype != w.dtype:
         x = x.to(w.dtype)
     if streams:
-        return linear_tc(x, w, out_dtype=out_dtype, swiglu=swiglu, _checked=True)
+        return linear_tc(x, w, out_dtype=out_dtype, swiglu=swiglu, _checked=True, act=act)
     if _own_gemm_fits(x, w, swiglu, out_dtype, "swiglu" if swiglu else "plain") and not partial_sums:
-        return gemm_tc(x, w, out_dtype=out_dtype, swiglu=swiglu)
+        return gemm_tc(x, w, out_dtype=out_dtype, swiglu=swiglu, act=act)
     if small:
         fn = _fn("linear_mma", "bn_linear_mma")
         splits = _mma_splits(M, N, K, n_sms(x.device))
@@ -963,7 +1018,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: 
         if swiglu:
             out = torch.empty((M, N // 2), dtype=out_dtype, device=x.device)
             _check(fn(_ptr(x), _ptr(w), _ptr(out), int(_DT[out_dtype]), int(M), int(N), int(K), int(N // 2),
-                      int(2), int(splits), *tail), "linear_mma")
+                      int(2 | act << 8), int(splits), *tail), "linear_mma")
             return out
         if partial_sums and splits > 1:
             out = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
@@ -1001,8 +1056,8 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, swiglu: 
         out = product() if PROFILE is None else _timed("library.matmul", product)
         out = out if out.dtype == out_dtype else out.to(out_dtype)
     if swiglu:
-        act = torch.empty((M, N // 2), dtype=out.dtype, device=x.device)
-        return silu_mul(out, act)
+        res = torch.empty((M, N // 2), dtype=out.dtype, device=x.device)
+        return glu_mul(out, res, act)
     return out
 
 
@@ -1066,6 +1121,174 @@ def mlstm_output(o: torch.Tensor, gain: torch.Tensor, g: torch.Tensor, g_stride:
     _check(_fn("mlstm", "bn_mlstm_output")(_ptr(o), _ptr(gain), int(_code(gain)), _ptr(g), int(g_stride), int(_DT[dtype]),
                                            int(o.shape[0]), int(n_heads), int(vdim), c_float(eps), _ptr(out), _stream()),
            "mlstm_output")
+    return out
+
+
+# ---- rotary pairs, parallel blocks, latents ------------------------------------------------------
+def rotary_pairs_append(x: torch.Tensor, freqs: torch.Tensor, tok_pos: torch.Tensor, *, xq: Optional[torch.Tensor] = None,
+                        q_off: int = 0, n_q_heads: int = 0,
+                        q_head_stride: int = 0, q_rot_off: int = 0, k_off: int = 0, n_k_heads: int = 0, k_head_stride: int = 0,
+                        k_rot_off: int = 0, k_row: int = 0, v_off: int = 0, v_head_stride: int = 0, v_row: int = 0,
+                        tok_seq: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
+                        page_table: Optional[torch.Tensor] = None, k_cache: Optional[torch.Tensor] = None,
+                        v_cache: Optional[torch.Tensor] = None) -> None:
+    """Rotary encoding in the interleaved pairing, in place: in every row of x the pairs (2i, 2i + 1), i < len(freqs),
+    of the rotated part of each query head (heads ``q_head_stride`` apart from ``q_off``, the part at ``q_rot_off``
+    inside a head) and of each key head (likewise) are turned by ``tok_pos * freqs[i]``.  With a cache the first
+    ``k_row`` numbers of every key head go there after rotation, and (``v_cache``) the first ``v_row`` numbers of
+    the heads at ``v_off`` as they were before it, so ``v_off`` may equal ``k_off``.  ``xq``: the tensor that holds
+    the query heads when it is not x (x then holds the key and value heads only)."""
+    _need(x, "x", dims=2)
+    xq = x if xq is None else xq
+    _need(xq, "xq", x.dtype, 2)
+    if xq.shape[0] < tok_pos.shape[0]:
+        raise KernelError("rotary_pairs_append: xq has fewer rows than there are tokens")
+    _need(freqs, "freqs", torch.float32, 1)
+    _need(tok_pos, "tok_pos", torch.int32, 1)
+    n = tok_pos.shape[0]
+    if x.shape[0] < n:
+        raise KernelError("rotary_pairs_append: x has fewer rows than there are tokens")
+    pt_stride = 0
+    if k_cache is not None:
+        for t, nm in ((tok_seq, "tok_seq"), (slots, "slots")):
+            _need(t, nm, torch.int32, 1)
+        _need(page_table, "page_table", torch.int32, 2)
+        _need(k_cache, "k_cache", x.dtype, 4)
+        if tuple(k_cache.shape[1:]) != (n_k_heads, PAGE, k_row):
+            raise KernelError(f"rotary_pairs_append: key cache {tuple(k_cache.shape)} is not [pages, {n_k_heads}, {PAGE}, {k_row}]")
+        if v_cache is not None:
+            _need(v_cache, "v_cache", x.dtype, 4)
+            if tuple(v_cache.shape[1:]) != (n_k_heads, PAGE, v_row) or v_cache.shape[0] != k_cache.shape[0]:
+                raise KernelError(f"rotary_pairs_append: value cache {tuple(v_cache.shape)} is not [pages, {n_k_heads}, {PAGE}, {v_row}]")
+        pt_stride = page_table.shape[1]
+    elif v_cache is not None:
+        raise KernelError("rotary_pairs_append: a value cache needs a key cache")
+    _check(_fn("rotary_pairs", "bn_rotary_pairs_append")(
+        _ptr(xq), int(xq.shape[1]), _ptr(x), int(_code(x)), int(n), int(x.shape[1]), _ptr(freqs), int(freqs.shape[0]), _ptr(tok_pos), int(q_off),
+        int(n_q_heads), int(q_head_stride), int(q_rot_off), int(k_off), int(n_k_heads), int(k_head_stride), int(k_rot_off),
+        int(k_row), int(v_off), int(v_head_stride), int(v_row), _ptr(tok_seq), _ptr(slots), _ptr(page_table), int(pt_stride),
+        _ptr(k_cache), _ptr(v_cache), _stream()), "rotary_pairs_append")
+
+
+def residual_add(x: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor] = None,
+                 cast: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """x += a (+ b) on the float32 residual; with ``cast`` returns the new rows in that type."""
+    _need(x, "x", torch.float32, 2)
+    _need(a, "a", dims=2)
+    if a.shape != x.shape or (b is not None and b.shape != x.shape):
+        raise KernelError("residual_add: shapes differ")
+    if b is not None:
+        _need(b, "b", dims=2)
+    out = torch.empty(x.shape, dtype=cast, device=x.device) if cast is not None and cast != torch.float32 else None
+    _check(_fn("norm", "bn_residual_add")(_ptr(x), _ptr(a), int(_code(a)), _ptr(b), int(_code(b)) if b is not None else 0,
+                                          _ptr(out), int(_code(out)) if out is not None else 0,
+                                          ctypes.c_longlong(x.numel()), _stream()), "residual_add")
+    return x if cast == torch.float32 else out
+
+
+def add_normed(x: torch.Tensor, y: torch.Tensor, wy: torch.Tensor, eps_y: float, w: Optional[torch.Tensor] = None,
+               eps: float = 0.0, out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """x += y / sqrt(mean(y^2) + eps_y) * wy on the float32 residual; with ``w`` also returns
+    x / sqrt(mean(x^2) + eps) * w of the new rows in ``out_dtype`` (the norm that reads them next)."""
+    _need(x, "x", torch.float32, 2)
+    _need(y, "y", dims=2)
+    _need(wy, "wy", dims=1)
+    if y.shape != x.shape or wy.shape[0] != x.shape[1] or (w is not None and w.shape[0] != x.shape[1]):
+        raise KernelError("add_normed: sizes do not fit")
+    out = None
+    if w is not None:
+        _need(w, "w", dims=1)
+        out = torch.empty(x.shape, dtype=out_dtype or y.dtype, device=x.device)
+    _check(_fn("norm", "bn_add_normed")(_ptr(x), _ptr(y), int(_code(y)), _ptr(wy), int(_code(wy)), c_float(eps_y), _ptr(w),
+                                        int(_code(w)) if w is not None else 0, c_float(eps), _ptr(out),
+                                        int(_code(out)) if out is not None else 0, int(x.shape[0]), int(x.shape[1]),
+                                        _stream()), "add_normed")
+    return out
+
+
+def rmsnorm_slices(x: torch.Tensor, eps: float, off0: int, len0: int, w0: torch.Tensor, off1: int = 0, len1: int = 0,
+                   w1: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """RMS norms of one or two slices of every row of x, in place, each with a gain of its own."""
+    _need(x, "x", dims=2)
+    _need(w0, "w0", dims=1)
+    if w1 is not None:
+        _need(w1, "w1", w0.dtype, 1)
+    if w0.shape[0] != len0 or (len1 > 0 and (w1 is None or w1.shape[0] != len1)):
+        raise KernelError("rmsnorm_slices: a gain does not fit its slice")
+    _check(_fn("norm", "bn_rmsnorm_slices")(_ptr(x), int(_code(x)), int(x.shape[1]), int(x.shape[0]), int(off0), int(len0),
+                                            _ptr(w0), int(off1), int(len1), _ptr(w1), int(_code(w0)), c_float(eps),
+                                            _stream()), "rmsnorm_slices")
+    return x
+
+
+# ---- gated delta rule ---------------------------------------------------------------------------
+def delta_state_floats(heads: int, kv_heads: int, dim: int, vdim: int, taps: int) -> int:
+    """Floats of one sequence's state: the heads' matrices, then the convolutions' last ``taps - 1`` inputs."""
+    return heads * dim * vdim + (taps - 1) * (2 * kv_heads * dim + heads * vdim)
+
+
+def delta_rule(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, conv_w: torch.Tensor, taps: int, b_off: int,
+               a_raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, state: torch.Tensor, tok_seq: torch.Tensor,
+               seq_start: torch.Tensor, slots: torch.Tensor, n_seqs: int, heads: int, kv_heads: int, dim: int,
+               vdim: int) -> torch.Tensor:
+    """The gated delta rule with a decay per head and key channel over the new tokens of every sequence, from
+    and into ``state`` ``[slots, delta_state_floats]`` (float32): short convolutions (``conv_w``: the tap tables
+    of the q, k and v channels one after another, ``[channels, taps]``) and SiLU on the projections in ``proj``,
+    unit q and k, beta = sigmoid of the ``heads`` numbers at ``b_off`` in ``proj``'s rows, decay = exp(-exp(``a_log``)
+    softplus(``a_raw`` + ``dt_bias``)) with ``a_raw`` the first ``heads * dim`` columns of a float32 matrix,
+    then S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q token by token.  Returns o, float32
+    ``[T, heads * vdim]``."""
+    _need(proj, "proj", dims=2)
+    _need(conv_w, "conv_w", dims=2)
+    _need(a_raw, "a_raw", torch.float32, 2)
+    _need(dt_bias, "dt_bias", conv_w.dtype, 1)
+    _need(a_log, "a_log", conv_w.dtype, 1)
+    _need(state, "state", torch.float32, 2)
+    for t, nm in ((tok_seq, "tok_seq"), (seq_start, "seq_start"), (slots, "slots")):
+        _need(t, nm, torch.int32, 1)
+    T = tok_seq.shape[0]
+    n_qk, n_v = kv_heads * dim, heads * vdim
+    if (conv_w.shape != (2 * n_qk + n_v, taps) or b_off + heads > proj.shape[1] or a_raw.shape[0] < T or a_raw.shape[1] < heads * dim
+            or dt_bias.shape[0] != heads * dim or a_log.shape[0] != heads or proj.shape[0] < T
+            or state.shape[1] != delta_state_floats(heads, kv_heads, dim, vdim, taps) or seq_start.shape[0] < n_seqs + 1):
+        raise KernelError("delta_rule: sizes do not fit")
+    if dim > 256:
+        raise KernelError(f"delta_rule: dim={dim} must be at most 256")
+    dev = proj.device
+    qn = torch.empty((T, n_qk), dtype=torch.float32, device=dev)
+    kn = torch.empty((T, n_qk), dtype=torch.float32, device=dev)
+    vc = torch.empty((T, n_v), dtype=torch.float32, device=dev)
+    decay = torch.empty((T, heads * dim), dtype=torch.float32, device=dev)
+    beta = torch.empty((T, heads), dtype=torch.float32, device=dev)
+    out = torch.empty((T, n_v), dtype=torch.float32, device=dev)
+    global LAUNCHES
+    if taps > 1:
+        LAUNCHES += 1  # the kernel that keeps the convolutions' last inputs
+    _check(_fn("delta_rule", "bn_delta_prepare")(
+        _ptr(proj), int(_code(proj)), int(T), int(proj.shape[1]), int(q_off), int(k_off), int(v_off), int(kv_heads), int(heads),
+        int(dim), int(vdim), int(taps), _ptr(conv_w), int(_code(conv_w)), _ptr(state), ctypes.c_longlong(state.shape[1]),
+        ctypes.c_longlong(heads * dim * vdim), _ptr(tok_seq), _ptr(seq_start), _ptr(slots), int(n_seqs), int(b_off),
+        _ptr(a_raw), int(a_raw.shape[1]), _ptr(dt_bias), _ptr(a_log), c_float(dim ** -0.5), _ptr(qn), _ptr(kn), _ptr(vc), _ptr(decay), _ptr(beta),
+        _stream()), "delta_prepare")
+    _check(_fn("delta_rule", "bn_delta_rule")(
+        _ptr(qn), _ptr(kn), _ptr(vc), _ptr(decay), _ptr(beta), _ptr(state), ctypes.c_longlong(state.shape[1]), _ptr(seq_start),
+        _ptr(slots), int(n_seqs), int(heads), int(kv_heads), int(dim), int(vdim), _ptr(out), _stream()), "delta_rule")
+    return out
+
+
+def delta_output(o: torch.Tensor, gain: torch.Tensor, gate: torch.Tensor, heads: int, vdim: int, eps: float,
+                 dtype: torch.dtype) -> torch.Tensor:
+    """Per head o / rms(o) (over ``vdim``, ``eps`` inside the root), times ``gain`` ``[vdim]`` (shared by the heads), times the
+    logistic function of ``gate`` (float32, a view ``[T, heads * vdim]`` with unit inner stride); result in ``dtype``."""
+    _need(o, "o", torch.float32, 2)
+    _need(gain, "gain", dims=1)
+    if (not gate.is_cuda or gate.dtype != torch.float32 or gate.stride(-1) != 1 or gate.shape[-1] != heads * vdim
+            or gain.shape[0] != vdim or o.shape[1] != heads * vdim):
+        raise KernelError("delta_output: gate or gain does not fit")
+    out = torch.empty((o.shape[0], heads * vdim), dtype=dtype, device=o.device)
+    _check(_fn("delta_rule", "bn_delta_output")(_ptr(o), _ptr(gain), int(_code(gain)), c_void_p(gate.data_ptr()),
+                                                int(gate.stride(0)), int(_DT[dtype]), int(o.shape[0]), int(heads), int(vdim),
+                                                c_float(eps), _ptr(out), _stream()), "delta_output")
     return out
 
 

@@ -59,7 +59,9 @@ class BuildContext:
 class KvRequest:
     """Keys and values per token that a mixer wants cached.  Runs whose requests are equal
     share one storage group; ``window`` > 0 means only the last ``window`` positions are kept, and
-    with ``keep_first`` also the positions below it.
+    with ``keep_first`` also the positions below it; ``chunk`` > 0 (in place of a window) means positions
+    are cut into chunks of so many and only those of the chunk a sequence is in are kept.
+    ``values_in_keys``: the values are a part of the key rows, so the group has no value plane.
     ``v_head_dim``: the width of a value head when it differs from a key head's (0: the same).
     The library's attention kernels take equal widths; a mixer with others brings its own."""
 
@@ -68,6 +70,8 @@ class KvRequest:
     window: int = 0
     v_head_dim: int = 0
     keep_first: int = 0
+    chunk: int = 0
+    values_in_keys: bool = False
 
     @property
     def v_dim(self) -> int:

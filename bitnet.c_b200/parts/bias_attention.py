@@ -9,7 +9,7 @@ import torch
 
 from ..csrc import ops
 from .base import KvRequest, Mixer, ParamSpec
-from .registry import register_mixer
+from .registry import build_part, register_mixer
 
 
 def distance_buckets(n_buckets: int, max_distance: int) -> torch.Tensor:
@@ -31,9 +31,11 @@ class BiasAttention(Mixer):
     square per head; k (normed) and v appended to the cache; for every head
     softmax(q k^T * scale + bias[bucket(distance)]) over the keys the window lets through; the head's
     output times the logistic function of its gate; output projection.  A run without projections of
-    keys and values reads the cache of the run its schedule entry names."""
+    keys and values reads the cache of the run its schedule entry names.  Optional: a position encoding on q
+    and k (``position``); chunks in place of the window (``chunk``); no value projection, the values being the
+    keys as projected, before the encoding (``values_are_keys``)."""
 
-    kernels = ("linear", "linear_mma", "linear_tc", "gemm_tc", "attention", "attention_prefill", "unit_norm")
+    kernels = ("linear", "linear_mma", "linear_tc", "gemm_tc", "attention", "attention_prefill", "unit_norm", "rotary_pairs")
     TILED_MIN_TOKENS = 16  # runs of new tokens from this many on take the tensor-core kernel (bfloat16)
     graph_safe = True
 
@@ -43,9 +45,19 @@ class BiasAttention(Mixer):
             raise ValueError(f"{spec.n_heads} heads are not a multiple of {spec.n_kv_heads} key/value heads")
         if not 0 < spec.head_dim <= 256 or not 0 < spec.v_head_dim <= 256:
             raise ValueError(f"head_dim={spec.head_dim} and v_head_dim={spec.v_head_dim} must be at most 256")
+        if spec.values_are_keys and (spec.v_head_dim != spec.head_dim or not spec.own_kv or spec.unit_norm):
+            raise ValueError("values that are the keys need equal widths, projections of their own and no unit norm")
+        if spec.chunk and (spec.window or spec.keep_first):
+            raise ValueError("chunks take the place of a window")
+        self.position = build_part("position", spec.position, build) if spec.position is not None else None
+        if self.position is not None and (spec.unit_norm or not hasattr(self.position, "apply")):
+            raise ValueError("this mixer takes a position encoding that offers ``apply`` (rotary_pairs), and no unit norm with it")
         self.w_in: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
         self.rel: Optional[torch.Tensor] = None
+
+    def children(self):
+        return {"position": self.position} if self.position is not None else {}
 
     @property
     def q_dim(self) -> int:
@@ -64,7 +76,8 @@ class BiasAttention(Mixer):
         p = {"q": ParamSpec((self.q_dim, s.width)), "o": ParamSpec((s.width, s.n_heads * s.v_head_dim))}
         if s.own_kv:
             p["k"] = ParamSpec((self.k_dim, s.width))
-            p["v"] = ParamSpec((self.v_dim, s.width))
+            if not s.values_are_keys:
+                p["v"] = ParamSpec((self.v_dim, s.width))
         if s.bias_buckets:
             p["rel"] = ParamSpec((s.bias_buckets, s.n_heads))
         if s.head_gate:
@@ -76,7 +89,11 @@ class BiasAttention(Mixer):
         parts = [tensors["q"]]
         self.k_off = self.v_off = self.g_off = 0
         at = self.q_dim
-        if s.own_kv:
+        if s.own_kv and s.values_are_keys:
+            parts.append(tensors["k"])
+            self.k_off = self.v_off = at
+            at += self.k_dim
+        elif s.own_kv:
             parts += [tensors["k"], tensors["v"]]
             self.k_off, self.v_off = at, at + self.k_dim
             at += self.k_dim + self.v_dim
@@ -100,7 +117,7 @@ class BiasAttention(Mixer):
     def cache_request(self) -> KvRequest:
         s = self.spec
         return KvRequest(n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window, v_head_dim=s.v_head_dim,
-                         keep_first=s.keep_first if s.window > 0 else 0)
+                         keep_first=s.keep_first if s.window > 0 else 0, chunk=s.chunk)
 
     def forward(self, h, ctx, kv, state):
         s = self.spec
@@ -108,7 +125,16 @@ class BiasAttention(Mixer):
         if kv.owner != s.own_kv:
             raise ValueError("a mixer with key/value projections owns its cache plane, one without reads another's")
         proj = ops.linear(h, self.w_in, out_dtype=self.build.dtype)
-        if not s.unit_norm:
+        if self.position is not None:
+            # values (the keys before the encoding, or projections of their own) to the cache, q and k encoded in
+            # place, keys to the cache: one launch
+            places = dict(q_off=0, n_q_heads=s.n_heads, q_head_stride=s.head_dim)
+            if kv.owner:
+                places.update(k_off=self.k_off, n_k_heads=s.n_kv_heads, k_head_stride=s.head_dim, k_row=s.head_dim,
+                              v_off=self.v_off, v_head_stride=s.v_head_dim, v_row=s.v_head_dim, tok_seq=ctx.tok_seq,
+                              slots=ctx.slots, page_table=kv.page_table, k_cache=kv.k, v_cache=kv.v)
+            self.position.apply(proj, ctx, **places)
+        elif not s.unit_norm:
             if kv.owner:  # queries and keys as the projections gave them
                 kv.append(proj, self.k_off, self.v_off, ctx)
         elif kv.owner:
@@ -128,11 +154,11 @@ class BiasAttention(Mixer):
             # softmax weights with 16 bits of mantissa
             ops.attention_prefill(proj, self.row, out, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, ctx.tile_seq,
                                   ctx.tile_row0, ctx.seq_start, ctx.seq_pos0, ctx.slots, kv.page_table, kv.k, kv.v,
-                                  keep_first=keep, rel=self.rel, gate=gate, gate_stride=self.row, precise=True)
+                                  keep_first=keep, rel=self.rel, gate=gate, gate_stride=self.row, precise=True, chunk=s.chunk)
         else:
             ops.attention_general(proj, self.row, out, n, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, ctx.tok_seq,
                                   ctx.tok_pos, ctx.slots, kv.page_table, kv.k, kv.v, keep_first=keep,
-                                  rel=self.rel, gate=gate, gate_stride=self.row,
-                                  max_keys=min(ctx.max_len, s.window + keep) if s.window > 0 else ctx.max_len)
+                                  rel=self.rel, gate=gate, gate_stride=self.row, chunk=s.chunk,
+                                  max_keys=min(ctx.max_len, s.chunk or (s.window + keep)) if (s.window > 0 or s.chunk > 0) else ctx.max_len)
         ctx.tap("attn_out", out)
         return ops.linear(out, self.w_o, out_dtype=torch.float32)

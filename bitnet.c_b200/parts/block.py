@@ -113,3 +113,62 @@ class PostNormBlock(Block):
         elif self.ffn_norm is not None and self.ffn_norm.weight is not None:
             h = self.ffn_norm.scaled_add_norm(x, alpha, None)
         return Cast(h)
+
+
+@register_block("parallel")
+class ParallelBlock(Block):
+    """x <- x + (mixer(h) + ffn(h)) with h = norm(x): one norm, both sublayers read its output, and their deltas
+    are summed before they meet the float32 stream.  Then, if the block has a ``side`` part, its input by token
+    id: x <- x + norm'(side(x)).  The norm of whoever reads the stream next is taken in the same pass as the
+    last addition when that reader says which it is (``next_norm``)."""
+
+    graph_safe = True  # as far as its parts are
+    accepts_normed = True
+
+    def __init__(self, spec, build):
+        super().__init__(spec, build)
+        self.norm = build_part("norm", spec.norm, build)
+        self.mixer = build_part("mixer", spec.mixer, build)
+        self.ffn = build_part("ffn", spec.ffn, build) if spec.ffn is not None else None
+        self.side = build_part("side", spec.side, build) if spec.side is not None else None
+
+    def children(self):
+        c = {"norm": self.norm, "mixer": self.mixer}
+        if self.ffn is not None:
+            c["ffn"] = self.ffn
+        if self.side is not None:
+            c["side"] = self.side
+        return c
+
+    def entry_norm(self):
+        return self.norm
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def state_request(self):
+        return self.mixer.state_request()
+
+    def forward(self, x, pending, ctx, kv, state, next_norm=None):
+        if isinstance(pending, Normed):
+            h = pending.value.dense() if isinstance(pending.value, ops.RowScaled) else pending.value
+        else:
+            h = self.norm.add_norm(x, pending, ctx)
+        ctx.tap("attn_norm", h)
+        d = self.mixer.forward(h, ctx, kv, state)
+        ctx.tap("attn_proj", d)
+        f = self.ffn.forward(h, ctx) if self.ffn is not None else None
+        if f is not None:
+            ctx.tap("ffn_out", f)
+        if self.side is None:
+            ops.residual_add(x, d, f)
+            return None
+        xc = ops.residual_add(x, d, f, cast=self.build.dtype)
+        y = self.side.delta(xc, ctx)
+        ctx.tap("side_out", y)
+        fused = next_norm if next_norm is not None and getattr(next_norm, "weight", None) is not None else None
+        s = self.side.spec
+        if fused is None:
+            ops.add_normed(x, y, self.side.gain, s.eps)
+            return None
+        return Normed(ops.add_normed(x, y, self.side.gain, s.eps, fused.weight, fused.spec.eps, self.build.dtype))

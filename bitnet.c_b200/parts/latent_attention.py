@@ -1,0 +1,116 @@
+"""Softmax attention through low-rank latents, with the latent itself as the cached key and value."""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..csrc import ops
+from .base import KvRequest, Mixer, ParamSpec
+from .registry import build_part, register_mixer
+
+
+@register_mixer("latent_attention")
+class LatentAttention(Mixer):
+    """c_q = norm(W_dq h), q = W_uq c_q, per head [plain | rotated]; W_dkv h = [latent | rotated key part], the
+    latent normed; per head k = [W_uk c | rotated part], v = W_uv c; softmax over the window; the head's output
+    times the logistic function of its gate; output projection.
+
+    Only the normed latent c and the rotated key part are cached, as one key row [c | k_rot] of one key/value
+    head, and attention runs on those rows directly: since (W_uk c) . q = c . (W_uk^T q), every head's plain
+    query part is carried into the latent space first (one small product per head), the scores are
+    q' . [c | k_rot] with q' = [W_uk^T q_plain | q_rot], the weighted sum of the rows' first kv_rank numbers is
+    the head's output in the latent space, and W_uv brings it back (another small product per head).  The
+    values are a part of the key rows, so the cache holds no value plane."""
+
+    kernels = ("linear", "linear_mma", "linear_tc", "gemm_tc", "attention", "attention_prefill", "rotary_pairs", "norm")
+    TILED_MIN_TOKENS = 16  # runs of new tokens from this many on take the tensor-core kernel (bfloat16)
+    graph_safe = True
+
+    def __init__(self, spec, build):
+        super().__init__(spec, build)
+        if min(spec.n_heads, spec.head_dim, spec.rot_dim, spec.v_head_dim, spec.q_rank, spec.kv_rank) <= 0:
+            raise ValueError("latent_attention: heads, head sizes and ranks must be positive")
+        if spec.kv_rank + spec.rot_dim > 2048:
+            raise ValueError(f"latent_attention: kv_rank + rot_dim = {spec.kv_rank + spec.rot_dim} must be at most 2048")
+        self.position = build_part("position", spec.position, build)
+        self.w_dq: Optional[torch.Tensor] = None
+
+    def children(self):
+        return {"position": self.position}
+
+    @property
+    def key_row(self) -> int:
+        return self.spec.kv_rank + self.spec.rot_dim
+
+    def params(self) -> Dict[str, ParamSpec]:
+        s = self.spec
+        p = {"dq": ParamSpec((s.q_rank, s.width)), "dq.norm": ParamSpec((s.q_rank,), init="ones"),
+             "uq": ParamSpec((s.n_heads * (s.head_dim + s.rot_dim), s.q_rank)),
+             "dkv": ParamSpec((self.key_row, s.width)), "dkv.norm": ParamSpec((s.kv_rank,), init="ones"),
+             "uk": ParamSpec((s.n_heads * s.head_dim, s.kv_rank)), "uv": ParamSpec((s.n_heads * s.v_head_dim, s.kv_rank)),
+             "o": ParamSpec((s.width, s.n_heads * s.v_head_dim))}
+        if s.head_gate:
+            p["g"] = ParamSpec((s.n_heads, s.width))
+        return p
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        s = self.spec
+        self.w_dq, self.g_dq = tensors["dq"], tensors["dq.norm"]
+        self.w_uq, self.g_dkv, self.w_o = tensors["uq"], tensors["dkv.norm"], tensors["o"]
+        # the latent, the rotated key part and the heads' gates are one product of the mixer's input
+        parts = [tensors["dkv"]] + ([tensors["g"]] if s.head_gate else [])
+        dt = parts[0].dtype if all(t.dtype == parts[0].dtype for t in parts) else torch.float32
+        self.g_off = self.key_row
+        at = self.key_row + (s.n_heads if s.head_gate else 0)
+        pad = -at % 8  # rows of the product's result stay 16-byte aligned
+        if pad:
+            parts.append(torch.zeros((pad, s.width), dtype=dt, device=parts[0].device))
+        self.w_kv = torch.cat([t.to(dt) for t in parts], dim=0).contiguous()
+        self.row = at + pad
+        # per head: W_uk as [dim, kv_rank] (plain query part -> latent space), W_uv as [vdim, kv_rank]
+        self.w_uk = tensors["uk"].reshape(s.n_heads, s.head_dim, s.kv_rank).contiguous()
+        self.w_uv = tensors["uv"].reshape(s.n_heads, s.v_head_dim, s.kv_rank).contiguous()
+
+    def cache_request(self) -> KvRequest:
+        s = self.spec
+        return KvRequest(n_kv_heads=1, head_dim=self.key_row, window=s.window, v_head_dim=s.kv_rank, values_in_keys=True)
+
+    def forward(self, h, ctx, kv, state):
+        s = self.spec
+        n = h.shape[0]
+        H, d, dr, rank, row = s.n_heads, s.head_dim, s.rot_dim, s.kv_rank, self.key_row
+        dt = self.build.dtype
+        cq = ops.linear(h, self.w_dq, out_dtype=dt)
+        ops.rmsnorm_slices(cq, s.norm_eps, 0, s.q_rank, self.g_dq)
+        q = ops.linear(cq, self.w_uq, out_dtype=dt)  # [n, H * (d + dr)]
+        ckv = ops.linear(h, self.w_kv, out_dtype=dt)  # [n, latent | rotated key part | gates | padding]
+        ops.rmsnorm_slices(ckv, s.norm_eps, 0, rank, self.g_dkv)
+        # rotate the heads' rotated query parts and the shared key part; the key row [c | k_rot] goes to the cache
+        self.position.apply(ckv, ctx, xq=q, q_off=0, n_q_heads=H, q_head_stride=d + dr, q_rot_off=d, k_off=0, n_k_heads=1,
+                            k_head_stride=row, k_rot_off=rank, k_row=row, tok_seq=ctx.tok_seq, slots=ctx.slots,
+                            page_table=kv.page_table, k_cache=kv.k)
+        # queries in the latent space: [W_uk^T q_plain | q_rot] per head
+        q3 = q.view(n, H, d + dr)
+        ql = torch.empty((n, H, row), dtype=q.dtype, device=q.device)
+        ql[:, :, :rank] = torch.bmm(q3[:, :, :d].transpose(0, 1), self.w_uk.to(q.dtype)).transpose(0, 1)
+        ql[:, :, rank:] = q3[:, :, d:]
+        if ctx.diag is not None:
+            ctx.tap("attn_q", lambda: ql.view(n, H * row))
+        out = torch.empty((n, H * rank), dtype=dt, device=h.device)
+        gate = ckv[:, self.g_off:] if s.head_gate else None
+        if (dt == torch.bfloat16 and not ctx.decode and ctx.tile_seq is not None and ctx.max_new >= self.TILED_MIN_TOKENS
+                and row % 16 == 0 and rank % 16 == 0 and row <= 256):
+            # runs of new tokens: 64 tokens of a sequence and a head per block on the tensor cores, the
+            # softmax weights with 16 bits of mantissa
+            ops.attention_prefill(ql, H * row, out, H, 1, row, s.scale, s.window, ctx.tile_seq, ctx.tile_row0, ctx.seq_start,
+                                  ctx.seq_pos0, ctx.slots, kv.page_table, kv.k, None, gate=gate, gate_stride=self.row,
+                                  precise=True, v_dim=rank)
+        else:
+            ops.attention_general(ql, H * row, out, n, H, 1, row, s.scale, s.window, ctx.tok_seq, ctx.tok_pos, ctx.slots,
+                                  kv.page_table, kv.k, None, gate=gate, gate_stride=self.row, v_dim=rank,
+                                  max_keys=min(ctx.max_len, s.window) if s.window > 0 else ctx.max_len)
+        ctx.tap("attn_out", out)
+        # back from the latent space: W_uv per head, heads side by side
+        o = torch.bmm(out.view(n, H, rank).transpose(0, 1), self.w_uv.to(dt).transpose(1, 2)).transpose(0, 1).contiguous()
+        return ops.linear(o.view(n, H * s.v_head_dim), self.w_o, out_dtype=torch.float32)

@@ -1,4 +1,4 @@
-"""Dense gated feed-forward (SwiGLU)."""
+"""Dense gated feed-forward (SwiGLU, or with the tanh form of GELU on the gate)."""
 from __future__ import annotations
 
 from typing import Dict
@@ -12,7 +12,9 @@ from .registry import register_ffn
 
 @register_ffn("gated_mlp")
 class GatedMlp(FeedForward):
-    """y = W_down (silu(W_gate h) * (W_up h))   (src/transformer/cpu.c:1247-1303)."""
+    """y = W_down (act(W_gate h) * (W_up h)), act = SiLU (src/transformer/cpu.c:1247-1303) or, by the spec's
+    ``activation``, the tanh form of GELU.  A width of the feed-forward that is no multiple of 8 is filled up with
+    rows of zeros, which add nothing."""
 
     kernels = ("linear", "linear_mma", "linear_tc", "gemm_tc", "act", "norm")
     graph_safe = True
@@ -20,8 +22,9 @@ class GatedMlp(FeedForward):
 
     def __init__(self, spec, build):
         super().__init__(spec, build)
-        if spec.activation != "silu":
-            raise ValueError(f"activation {spec.activation!r} is not built; this feed-forward uses 'silu'")
+        if spec.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {spec.activation!r} is not built; known: {', '.join(sorted(ops.ACTIVATIONS))}")
+        self.act = ops.ACTIVATIONS[spec.activation]
 
     def params(self) -> Dict[str, ParamSpec]:
         s = self.spec
@@ -31,12 +34,19 @@ class GatedMlp(FeedForward):
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         g, u = tensors["gate"], tensors["up"]
         dt = g.dtype if g.dtype == u.dtype else torch.float32
+        down = tensors["down"]
+        pad = -g.shape[0] % 8
+        if pad:
+            zeros = torch.zeros((pad, g.shape[1]), dtype=dt, device=g.device)
+            g, u = torch.cat([g.to(dt), zeros]), torch.cat([u.to(dt), zeros])
+            down = torch.cat([down, torch.zeros((down.shape[0], pad), dtype=down.dtype, device=down.device)], dim=1).contiguous()
         # gate and up rows in alternating blocks of 8: one product gives both, and with few rows
         # its epilogue applies the activation (the reference stacks gate and up on upload,
         # src/gpu_cuda.cu:11521-11558, and fuses gate/up + SiLU for decode, src/gpu_cuda.cu:4547)
         self.w_gate_up = ops.interleave_gate_up(g.to(dt), u.to(dt))
-        self.w_down = tensors["down"]
+        self.w_down = down
 
     def forward(self, h, ctx, sink=None):
-        act = ops.linear(h, self.w_gate_up, out_dtype=self.build.dtype, swiglu=True)
-        return ops.linear(act, self.w_down, out_dtype=self.build.dtype, sink=sink)
+        act = ops.linear(h, self.w_gate_up, out_dtype=self.build.dtype, swiglu=True, act=self.act)
+        out_dtype = torch.float32 if getattr(self.spec, "wide_output", False) else self.build.dtype
+        return ops.linear(act, self.w_down, out_dtype=out_dtype, sink=sink)

@@ -46,3 +46,50 @@ class NoPosition(Position):
 
     def rotate(self, x, n_heads, head_dim, ctx):
         return None
+
+
+def pair_frequencies(spec) -> np.ndarray:
+    """The table of a ``RotaryPairsSpec``: base^(-2i/dims) for i < dims/2 in double precision, long wavelengths
+    slowed down as ``scaling`` = (factor, low, high, original) says (wavelength l = 2 pi / f: f stays where
+    l < original / high, becomes f / factor where l > original / low, and in between the blend
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low)); rounded to float32 once."""
+    i = np.arange(spec.dims // 2, dtype=np.float64)
+    f = np.float64(spec.base) ** (-2.0 * i / spec.dims)
+    if spec.scaling is not None:
+        factor, low, high, original = (float(v) for v in spec.scaling)
+        wavelength = 2.0 * np.pi / f
+        s = (original / wavelength - low) / (high - low)
+        blend = (1.0 - s) * f / factor + s * f
+        f = np.where(wavelength < original / high, f, np.where(wavelength > original / low, f / factor, blend))
+    return f.astype(np.float32)
+
+
+@register_position("rotary_pairs")
+class RotaryPairs(Position):
+    """Rotary encoding in the interleaved pairing with a table of frequencies (``pair_frequencies``): the pair
+    (2i, 2i + 1) of the rotated part of a head is turned by position * f_i, angles in float32.  Besides
+    ``rotate`` it offers ``apply``, which places the rotated part anywhere inside the heads of two tensors and
+    writes keys (and unrotated values) into the cache in the same launch."""
+
+    kernels = ("rotary_pairs",)
+    graph_safe = True
+
+    def __init__(self, spec, build):
+        super().__init__(spec, build)
+        if spec.dims % 2 or spec.dims <= 0 or spec.dims > 512:
+            raise ValueError(f"rotary dims={spec.dims} must be even and at most 512")
+        self._table = pair_frequencies(spec)
+        self._freqs = None
+
+    def freqs(self, device):
+        if self._freqs is None or self._freqs.device != device:
+            import torch
+            self._freqs = torch.from_numpy(self._table).to(device)
+        return self._freqs
+
+    def rotate(self, x, n_heads, head_dim, ctx):
+        ops.rotary_pairs_append(x, self.freqs(x.device), ctx.tok_pos, q_off=0, n_q_heads=n_heads, q_head_stride=head_dim)
+
+    def apply(self, x, ctx, **places):
+        """``ops.rotary_pairs_append`` with this encoding's table and the step's positions."""
+        ops.rotary_pairs_append(x, self.freqs(x.device), ctx.tok_pos, **places)

@@ -13,7 +13,7 @@ from ..config.spec import ConfigError
 from .base import BuildContext, Part
 
 _REGISTRIES: Dict[str, Dict[str, Type[Part]]] = {
-    "mixer": {}, "ffn": {}, "norm": {}, "position": {}, "block": {}, "head": {},
+    "mixer": {}, "ffn": {}, "norm": {}, "position": {}, "block": {}, "head": {}, "side": {},
 }
 
 
@@ -45,6 +45,10 @@ def register_position(kind: str):
 
 def register_block(kind: str):
     return _register("block", kind)
+
+
+def register_side(kind: str):
+    return _register("side", kind)
 
 
 def register_head(kind: str):

@@ -102,7 +102,12 @@ def load_weights(model_dir: str, table: Mapping[str, "ParamSpec"], tensor_name: 
                 if n in where:
                     dup.append(f"tensor '{n}' is stored in two shards")
                 where[n] = f
-        wanted = {tensor_name(path): path for path in table}
+        # several parameters may be one tensor of the file (a table that all blocks share): it is read once and
+        # every one of them is bound to the same device tensor
+        sharers: Dict[str, List[str]] = {}
+        for path in table:
+            sharers.setdefault(tensor_name(path), []).append(path)
+        wanted = {n: paths[0] for n, paths in sharers.items()}
         missing = sorted(n for n, path in wanted.items() if n not in where and not table[path].optional)
         unexpected = sorted(n for n in where if n not in wanted)
         mismatched: List[str] = []
@@ -117,6 +122,9 @@ def load_weights(model_dir: str, table: Mapping[str, "ParamSpec"], tensor_name: 
             elif is_int != bool(p.integer):
                 mismatched.append(f"{n}: file has {e.dtype}, model needs "
                                   f"{'an integer table' if p.integer else 'floating point'}")
+            for other in sharers[n][1:]:
+                if tuple(table[other].shape) != tuple(p.shape) or bool(table[other].integer) != bool(p.integer):
+                    mismatched.append(f"{n}: parameters '{path}' and '{other}' share it but differ in shape or kind")
         if missing or unexpected or mismatched or dup:
             raise WeightsError(model_dir, missing, unexpected, mismatched, dup)
         out: Dict[str, torch.Tensor] = {}
@@ -130,6 +138,9 @@ def load_weights(model_dir: str, table: Mapping[str, "ParamSpec"], tensor_name: 
             if keep == torch.float32 and dtype == torch.bfloat16 and t.dim() >= 2:
                 wide.append(n)
             out[path] = t.to(device=device, dtype=keep).contiguous()
+        for n, paths in sharers.items():
+            for other in paths[1:]:
+                out[other] = out[paths[0]]
         if wide:
             # a tensor stored in 32-bit stays 32-bit; say what that costs instead of doing it silently
             warnings.warn(f"'{model_dir}': {len(wide)} matrices are stored in 32-bit floating point and are kept so "

@@ -115,16 +115,26 @@ def random_parameters(spec, tensor_name, seed: int, dtype: torch.dtype, matrix_s
     embedding N(0, matrix_std), norm gains 1 + N(0, norm_std), integer tables zero.  The values
     depend on the seed and on the tensor's name in the file only."""
     from ..engine.model import parameter_table
+    made: Dict[str, torch.Tensor] = {}  # parameters that share a tensor of the file get the same one
     for path, p in parameter_table(spec).items():
         name = tensor_name(path)
-        if p.init == "ones":
-            yield path, name, random_tensor(seed, name, p.shape, 1.0, norm_std, dtype, device)
-        elif p.init == "normal":
-            yield path, name, random_tensor(seed, name, p.shape, 0.0, matrix_std, dtype, device)
-        elif p.init == "zeros":
-            yield path, name, torch.zeros(p.shape, dtype=torch.int32 if p.integer else dtype, device=device)
-        else:
-            raise ValueError(f"parameter '{path}' has unknown init '{p.init}'")
+        if name in made:
+            yield path, name, made[name]
+            continue
+        for item in _draw(path, name, p, seed, dtype, matrix_std, norm_std, device):
+            made[name] = item[2]
+            yield item
+
+
+def _draw(path, name, p, seed, dtype, matrix_std, norm_std, device):
+    if p.init == "ones":
+        yield path, name, random_tensor(seed, name, p.shape, 1.0, norm_std, dtype, device)
+    elif p.init == "normal":
+        yield path, name, random_tensor(seed, name, p.shape, 0.0, matrix_std, dtype, device)
+    elif p.init == "zeros":
+        yield path, name, torch.zeros(p.shape, dtype=torch.int32 if p.integer else dtype, device=device)
+    else:
+        raise ValueError(f"parameter '{path}' has unknown init '{p.init}'")
 
 
 def write_random_model(folder: str, config: Dict[str, Any], seed: int, dtype: str = "bfloat16",
@@ -145,8 +155,11 @@ def write_random_model(folder: str, config: Dict[str, Any], seed: int, dtype: st
     os.makedirs(folder, exist_ok=True)
 
     def tensors():
+        seen = set()
         for _path, name, t in random_parameters(spec, arch.tensor_name, seed, store, matrix_std, norm_std, device):
-            yield name, t
+            if name not in seen:
+                seen.add(name)
+                yield name, t
 
     write_safetensors(os.path.join(folder, "model.safetensors"), tensors(),
                       metadata={"format": "pt", "seed": str(seed)})
