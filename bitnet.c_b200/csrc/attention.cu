@@ -79,14 +79,16 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
   __syncthreads();
 
   constexpr int VN = Vec16<T>::N;
-  constexpr int MAX_D = 2;  // output dims per thread: v_dim <= 256
+  constexpr int MAX_D = 8;  // output dims per thread when a row is not read in 16-byte pieces: v_dim <= 1024
   // Weighted sum of the values.  Rows of whole 16-byte pieces: a row is read by v_dim / VN threads,
   // one piece each, and the rows of a chunk are shared out over the groups of such threads; the
   // groups' sums meet in shared memory at the end.  Other widths: one thread per dimension.
   const bool wide = (v_dim % VN) == 0 && (v_row % VN) == 0 && v_dim / VN <= ATT_THREADS;
   const int per_row = wide ? v_dim / VN : 1, groups = wide ? ATT_THREADS / per_row : 1;
   const int piece = threadIdx.x % per_row, group = threadIdx.x / per_row;
-  float acc[MAX_D] = {0.f, 0.f};
+  float acc[MAX_D];
+#pragma unroll
+  for (int r = 0; r < MAX_D; ++r) acc[r] = 0.f;
   float accv[VN];
 #pragma unroll
   for (int e = 0; e < VN; ++e) accv[e] = 0.f;
@@ -226,12 +228,12 @@ extern "C" int bn_attention_general_ex(const void* q, int q_stride, void* out, i
   if (n_splits < 1 || n_splits > 64 || (n_splits > 1 && !part)) return BN_ERR_BAD_ARG;
   if (n_splits == 1) part = nullptr;
   if (v_row <= 0) v_row = v_dim;
-  // value rows of whole 16-byte pieces may be up to 128 pieces wide; others are one dimension per thread, twice
+  // value rows of whole 16-byte pieces may be up to 128 pieces wide; others are one dimension per thread, eight times
   const int vn = dtype == BN_F32 ? 4 : 8;
   const bool wide = v_dim % vn == 0 && v_row % vn == 0 && v_dim / vn <= ATT_THREADS;
   if (head_dim <= 0 || head_dim > 2048 || n_kv_heads <= 0 || n_heads % n_kv_heads || window < 0 || keep_first < 0 ||
       chunk < 0 || (chunk > 0 && (window > 0 || keep_first > 0)) || v_dim <= 0 || v_row < v_dim ||
-      (!wide && v_dim > 2 * ATT_THREADS) || (rel && n_rel <= 0))
+      (!wide && v_dim > 8 * ATT_THREADS) || (rel && n_rel <= 0))
     return BN_ERR_BAD_ARG;
   if (n_heads > 65535) return BN_ERR_BAD_ARG;
   dim3 grid(n_tokens, n_heads, n_splits);

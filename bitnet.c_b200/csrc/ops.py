@@ -350,10 +350,8 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
     if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, head_dim) or tuple(k_cache.shape[:3]) != tuple(v_cache.shape[:3]):
         raise KernelError(f"attention: cache {tuple(k_cache.shape)} / {tuple(v_cache.shape)} is not "
                           f"[pages, {n_kv_heads}, {PAGE}, {head_dim} / value width]")
-    piece = 4 if q.dtype == torch.float32 else 8
-    if not 0 < head_dim <= 2048 or (v_dim > 256 and (v_dim % piece or (v_row or v_dim) % piece or v_dim // piece > 128)):
-        raise KernelError(f"attention: head_dim={head_dim} (at most 2048) or the value width {v_dim} (at most 256, or whole "
-                          f"16-byte pieces up to 128 of them) is not supported")
+    if not 0 < head_dim <= 2048 or v_dim > 1024:
+        raise KernelError(f"attention: head_dim={head_dim} (at most 2048) or the value width {v_dim} (at most 1024) is not supported")
     if chunk < 0 or (chunk > 0 and (window > 0 or keep_first > 0)):
         raise KernelError("attention: chunks take the place of a window")
     if n_heads % n_kv_heads:

@@ -283,17 +283,25 @@ _ROUNDED = {}
 
 def _check(got, cfg, w, reqs, plain, dtype, what):
     """float32: every position within 1e-4 of the plain logits (relative to the largest).  bfloat16: the bound
-    of a request is three times what rounding the stored activations does to the plain statement."""
+    of a request is three times what rounding the stored activations does to the plain statement, taken at the
+    request's 80th percentile of positions (sharp models answer single roundings in a recurrence or next to
+    a mask's edge with gaps several times the typical one, in the engine at other places than in the rounded
+    plain statement); at most a fifth of a request's positions may lie beyond it, none beyond three times the
+    largest gap."""
     if dtype == "float32":
         return compare(got, plain, lambda ref: TOL_F32 * max(1.0, float(np.abs(ref).max())), what)
-    bounds = {}
-    for r in got:
+    for r, per_pos in got.items():
         key = (cfg["vocab"], r, tuple(reqs[r]))
         if key not in _ROUNDED:
             _ROUNDED[key] = pl.forward(cfg, w, reqs[r], round_fn=pl.to_bf16)
-        bounds[r] = BF16_GAP_FACTOR * float(np.abs(plain[r] - _ROUNDED[key]).max())
-        assert bounds[r] < 0.1 * float(np.abs(plain[r]).max()), "the test model is too rough for bfloat16"
-    return compare(got, plain, bounds, what)
+        gap = np.abs(plain[r] - _ROUNDED[key]).max(axis=1)
+        bound = BF16_GAP_FACTOR * float(np.percentile(gap, 80))
+        assert bound < 0.1 * float(np.abs(plain[r]).max()), "the test model is too rough for bfloat16"
+        err = np.array([np.abs(row.astype(np.float64) - plain[r][p]).max() for p, row in sorted(per_pos.items())])
+        assert np.isfinite(err).all() and err.max() <= BF16_GAP_FACTOR * float(gap.max()), f"{what}: request {r}"
+        beyond = int((err > bound).sum())
+        assert beyond <= max(1, len(err) // 5), (f"{what}: request {r}: {beyond} of {len(err)} positions beyond {bound:.3e}; "
+                                                 f"first at {sorted(per_pos)[int(np.argmax(err > bound))]}")
 
 
 def _poison(cache):
