@@ -9,7 +9,7 @@ import pytest
 import bitnet_c_b200 as bn
 import lotilix_cases as lc
 import plain_lotilix as pl
-from helpers import random_tokens, replay, trace_batches, trace_chunks, trace_tail, trace_whole
+from helpers import TOL_F32, random_tokens, replay, trace_batches, trace_chunks, trace_tail, trace_whole
 from test_lotilix_gpu import _check, _poison
 
 pytestmark = pytest.mark.gpu
@@ -58,6 +58,12 @@ def test_a_configuration_drawn_at_random_steps_like_the_plain_statement(tmp_path
     V = cfg["vocab"]
     reqs = {"a": random_tokens(seed, 230, V), "b": random_tokens(seed + 50, 1, V), "c": random_tokens(seed + 99, 70, V)}
     plain = {r: pl.forward(cfg, w, t) for r, t in reqs.items()}
+    # a model drawn at random may answer single-precision rounding at single places with far more than 1e-4 of
+    # its logits (a unit norm or a sharp softmax row behind a nearly empty state): how much, place by place, shows
+    # when the plain statement runs with weights moved by 1e-7 of their size; float32 is allowed 30 times that
+    rng = np.random.default_rng(seed)
+    moved = {k: a * (1.0 + 1e-7 * rng.standard_normal(a.shape)) for k, a in w.items()}
+    slack = {r: 30.0 * np.abs(pl.forward(cfg, moved, t) - plain[r]).max(axis=1) for r, t in reqs.items()}
     for dtype in ("float32", "bfloat16") if seed % 2 == 0 else ("float32",):
         model = bn.load_model(folder, dtype=dtype)
         cache = model.new_cache(max_tokens=64 * 10, max_seqs=3)
@@ -65,5 +71,13 @@ def test_a_configuration_drawn_at_random_steps_like_the_plain_statement(tmp_path
         for what, steps in (("whole", trace_whole(reqs)), ("last 25 one by one", trace_tail(reqs, 25)),
                             ("pieces", trace_chunks(reqs, pieces=(3, 64, 17, 1))),
                             ("an unequal batch", trace_batches([{"a": (reqs["a"], 12), "c": (reqs["c"], 30), "b": (reqs["b"], 0)}]))):
-            _check(replay(model, cache, steps), cfg, w, reqs, plain, dtype, f"seed {seed}: {what}, {dtype}")
+            got = replay(model, cache, steps)
+            if dtype == "bfloat16":
+                _check(got, cfg, w, reqs, plain, dtype, f"seed {seed}: {what}, {dtype}", rough_ok=True)
+                continue
+            for r, per_pos in got.items():
+                for p, row in sorted(per_pos.items()):
+                    err = float(np.abs(row.astype(np.float64) - plain[r][p]).max())
+                    assert err <= TOL_F32 * max(1.0, float(np.abs(plain[r]).max())) + slack[r][p], \
+                        f"seed {seed}: {what}: request {r} position {p}: max |diff| {err:.3e}"
         model.check_kernels()
