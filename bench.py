@@ -459,6 +459,41 @@ DESIGN_SIZES = {
 }
 
 
+def lotilix_sizes(width, heads, kv_heads, dim, rot_dim, q_rank, kv_rank, d_heads, d_dim, d_vdim, taps, low_rank, ff, side_dim,
+                  window, chunk, vocab):
+    """A Lotilix configuration of four layers (latent attention, delta rule, chunked attention on unrotated keys,
+    latent attention; every layer with its dense feed-forward and per-token input) and the Llama configuration of
+    the same width, heads, layers, vocabulary and feed-forward width."""
+    rot = {"base": 1e6, "dims": rot_dim}
+    latent = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": dim, "q_rank": q_rank, "kv_rank": kv_rank,
+              "scale": (dim + rot_dim) ** -0.5, "rot": rot, "mask": {"size": window}}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+           "rot": {"base": 5e5, "dims": dim, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}},
+           "mask": {"size": chunk}}
+    delta = {"heads": d_heads, "kv_heads": d_heads, "dim": d_dim, "vdim": d_vdim, "conv": taps, "decay_rank": low_rank,
+             "gate_rank": low_rank}
+    mlp = {"kind": "dense", "ff": ff}
+    layers = [{"type": "latent_attention", "mixer": dict(latent), "mlp": mlp}, {"type": "channel_delta", "mixer": delta, "mlp": mlp},
+              {"type": "attention", "mixer": att, "mlp": mlp}, {"type": "latent_attention", "mixer": dict(latent), "mlp": mlp}]
+    lot = {"architecture": "Lotilix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "token_side": {"dim": side_dim},
+           "layers": layers, "max_positions": 8192}
+    llama = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": width, "intermediate_size": ff,
+             "num_hidden_layers": len(layers), "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": dim,
+             "vocab_size": vocab, "max_position_embeddings": 8192, "rope_theta": 500000.0, "rms_norm_eps": 1e-5,
+             "tie_word_embeddings": False, "hidden_act": "silu"}
+    return lot, llama
+
+
+LOTILIX_SIZES = {
+    "w1024": dict(width=1024, heads=8, kv_heads=2, dim=128, rot_dim=64, q_rank=384, kv_rank=192, d_heads=8, d_dim=128, d_vdim=128,
+                  taps=4, low_rank=64, ff=4096, side_dim=128, window=1024, chunk=1024, vocab=32000),
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, rot_dim=64, q_rank=768, kv_rank=192, d_heads=16, d_dim=128, d_vdim=128,
+                  taps=4, low_rank=64, ff=8192, side_dim=256, window=1024, chunk=1024, vocab=32000),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, rot_dim=64, q_rank=1536, kv_rank=512, d_heads=32, d_dim=128, d_vdim=128,
+                  taps=4, low_rank=128, ff=14336, side_dim=256, window=1024, chunk=1024, vocab=32000),
+}
+
+
 def kernel_classes(model, vocab, tokens, batch, prompt_len):
     """Device time by entry point (ms) of one step of ``tokens`` prompt tokens and of one decode step of
     ``batch`` sequences behind prompts of ``prompt_len``, each kernel between two events (no graph, so the
@@ -499,7 +534,7 @@ def kernel_classes(model, vocab, tokens, batch, prompt_len):
 
 
 def run_design(args):
-    """``--design fesorax``: prefill and decode throughput of the Fesorax design at layer sizes of real
+    """``--design fesorax | lotilix``: prefill and decode throughput of that design at layer sizes of real
     models (random weights, bfloat16), beside the Llama decoder of equal width, heads, layers, vocabulary and
     feed-forward work per token, with each step's device time by kernel entry point."""
     import torch
@@ -508,13 +543,15 @@ def run_design(args):
     rec = {"metric": "prefill and decode tokens/s of the Fesorax design beside Llama at equal size", "impl": "ours",
            "dtype": "bf16", "data": "synthetic", "n_gpus": 1, "peaks": pk, "prefill_tokens": PREFILL_TOKENS,
            "decode_batch": args.batch, "decode_prompt": PROMPT_LEN, "sizes": {}}
-    names = [n for n in DESIGN_SIZES if not args.sizes or n in args.sizes.split(",")]
+    sizes, maker = (LOTILIX_SIZES, lotilix_sizes) if args.design == "lotilix" else (DESIGN_SIZES, fesorax_sizes)
+    rec["metric"] = rec["metric"].replace("Fesorax", args.design.capitalize())
+    names = [n for n in sizes if not args.sizes or n in args.sizes.split(",")]
     for name in names:
-        fes, llama = fesorax_sizes(**DESIGN_SIZES[name])
+        fes, llama = maker(**sizes[name])
         row = {}
-        for label, cfg in (("fesorax", fes), ("llama", llama)):
+        for label, cfg in ((args.design, fes), ("llama", llama)):
             model = Model.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", norm_std=0.0)
-            shim = {"vocab_size": DESIGN_SIZES[name]["vocab"], "max_position_embeddings": 4096}
+            shim = {"vocab_size": sizes[name]["vocab"], "max_position_embeddings": 4096}
             pre_ms = run_prefill(model, shim)
             r = run_decode(model, shim, args.batch, args.steps, max(3, args.warmup))
             row[label] = {"prefill_ms": round(pre_ms, 3), "prefill_tokens_per_s": round(PREFILL_TOKENS / pre_ms * 1e3, 1),
@@ -546,7 +583,7 @@ def main():
                          "(comparisons, profiling)")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                     help="compute type of the main decode run (float32: profiling of the 32-bit path, with --skip-points)")
-    ap.add_argument("--design", choices=["fesorax"],
+    ap.add_argument("--design", choices=["fesorax", "lotilix"],
                     help="measure another design of the library beside Llama at equal size instead (prefill, decode, "
                          "time by kernel); the default workload and its record stay as they are")
     ap.add_argument("--sizes", default="", help="with --design: which size sets, with commas (default: all)")

@@ -100,22 +100,25 @@ __global__ void delta_tail_kernel(const T* __restrict__ proj, int stride, int q_
     if (j < taps - 1) tail[(size_t)j * n_ch + c] = keep[j];
 }
 
-// The recurrence, token by token.  A block of four warps per (sequence, head, 32 value columns): a lane
-// holds its column of S in registers, a warp a quarter of the rows (RW each); the tokens' q, k and decay
-// rows pass through shared memory three tokens deep, so that one barrier per token is enough.
-// Since o = (gS)^T q + (k . q) u, both read-outs of the decayed state are taken in one pass over the rows.
+// The recurrence, token by token.  A block of eight warps per (sequence, head, 32 value columns): a lane
+// holds its column of S in registers, a warp an eighth of the rows (RW each, a multiple of 4); the tokens' q, k
+// and decay rows pass through shared memory three tokens deep (rows past dim are zeros, so that the state rows
+// there stay zero and the loops need no bounds), read four numbers at a time, and one barrier per token is
+// enough.  Since o = (gS)^T q + (k . q) u, both read-outs of the decayed state are taken in one pass over the rows.
+#define DR_WARPS 8
+#define DR_THREADS (DR_WARPS * 32)
 template <int RW>
-__global__ void __launch_bounds__(128) delta_rule_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
-                                                         const float* __restrict__ vc, const float* __restrict__ decay,
-                                                         const float* __restrict__ beta, float* __restrict__ state,
-                                                         size_t state_stride, const int* __restrict__ seq_start,
-                                                         const int* __restrict__ slots, int heads, int kv_heads, int dim,
-                                                         int vdim, int col_tiles, float* __restrict__ out) {
+__global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
+                                                                const float* __restrict__ vc, const float* __restrict__ decay,
+                                                                const float* __restrict__ beta, float* __restrict__ state,
+                                                                size_t state_stride, const int* __restrict__ seq_start,
+                                                                const int* __restrict__ slots, int heads, int kv_heads, int dim,
+                                                                int vdim, int col_tiles, float* __restrict__ out) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float sm[];
-  float* in = sm;                        // [3][3 * dim]: q, k, decay of a token
-  float* red = sm + 9 * dim;             // [2][4][65]: the warps' partial read-outs and k . q
+  constexpr int ROWS = DR_WARPS * RW;    // rows of the padded state, >= dim
+  __shared__ __align__(16) float in[3][3][ROWS];       // [token % 3][q, k, decay][row]
+  __shared__ float red[2][DR_WARPS][65];               // the warps' partial read-outs and k . q
   const int tile = blockIdx.x % col_tiles, h = (blockIdx.x / col_tiles) % heads, s = blockIdx.x / (col_tiles * heads);
   const int g = h / (heads / kv_heads);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -128,71 +131,72 @@ __global__ void __launch_bounds__(128) delta_rule_kernel(const float* __restrict
 #pragma unroll
   for (int i = 0; i < RW; ++i) S[i] = (live && row0 + i < dim) ? S_g[(size_t)(row0 + i) * vdim + col] : 0.f;
   const int n_qk = kv_heads * dim;
-  auto stage = [&](int tok, int buf) {  // the rows of token `tok` into buffer `buf`
+  // a thread fetches at most one row of a token: ROWS <= DR_THREADS
+  const int my_row = threadIdx.x;
+  const bool fetches = my_row < ROWS;
+  const bool in_dim = my_row < dim;
+  auto fetch = [&](int tok, float& q, float& k, float& d) {
     const size_t t = (size_t)(start + tok);
-    float* b = in + (size_t)buf * 3 * dim;
-    for (int i = threadIdx.x; i < dim; i += 128) {
-      b[i] = qn[t * n_qk + (size_t)g * dim + i];
-      b[dim + i] = kn[t * n_qk + (size_t)g * dim + i];
-      b[2 * dim + i] = decay[(t * heads + h) * dim + i];
-    }
+    q = in_dim ? qn[t * n_qk + (size_t)g * dim + my_row] : 0.f;
+    k = in_dim ? kn[t * n_qk + (size_t)g * dim + my_row] : 0.f;
+    d = in_dim ? decay[(t * heads + h) * dim + my_row] : 0.f;
   };
-  if (n > 0) stage(0, 0);
-  if (n > 1) stage(1, 1);
+  auto put = [&](int buf, float q, float k, float d) {
+    if (fetches) { in[buf][0][my_row] = q; in[buf][1][my_row] = k; in[buf][2][my_row] = d; }
+  };
+  {
+    float q, k, d;
+    if (n > 0) { fetch(0, q, k, d); put(0, q, k, d); }
+    if (n > 1) { fetch(1, q, k, d); put(1, q, k, d); }
+  }
   __syncthreads();
+  float v_next = (n > 0 && live) ? vc[(size_t)start * heads * vdim + (size_t)h * vdim + col] : 0.f;
+  float b_next = n > 0 ? beta[(size_t)start * heads + h] : 0.f;
   for (int tok = 0; tok < n; ++tok) {
     const size_t t = (size_t)(start + tok);
-    const float* b = in + (size_t)(tok % 3) * 3 * dim;
-    const float v = live ? vc[t * heads * vdim + (size_t)h * vdim + col] : 0.f;
-    const float bt = beta[t * heads + h];
-    float nq[2], nk[2], ng[2];  // the rows of the token after next, asked for now and put down after the barrier
-    if (tok + 2 < n) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int i = threadIdx.x + e * 128;
-        if (i < dim) {
-          nq[e] = qn[(t + 2) * n_qk + (size_t)g * dim + i];
-          nk[e] = kn[(t + 2) * n_qk + (size_t)g * dim + i];
-          ng[e] = decay[((t + 2) * heads + h) * dim + i];
-        }
-      }
+    const int buf = tok % 3;
+    const float v = v_next, bt = b_next;
+    if (tok + 1 < n) {
+      v_next = live ? vc[(t + 1) * heads * vdim + (size_t)h * vdim + col] : 0.f;
+      b_next = beta[(t + 1) * heads + h];
     }
+    float nq = 0.f, nk = 0.f, nd = 0.f;  // the rows of the token after next, asked for now and put down after the barrier
+    if (tok + 2 < n && fetches) fetch(tok + 2, nq, nk, nd);
     float pk = 0.f, pq = 0.f, kq = 0.f;
+    float kreg[RW];
 #pragma unroll
-    for (int i = 0; i < RW; ++i) {
-      if (row0 + i < dim) {
-        const float q = b[row0 + i], k = b[dim + row0 + i];
-        const float sd = S[i] * b[2 * dim + row0 + i];
-        S[i] = sd;
-        pk = fmaf(sd, k, pk);
-        pq = fmaf(sd, q, pq);
-        kq = fmaf(k, q, kq);
+    for (int i = 0; i < RW; i += 4) {
+      const float4 q4 = *reinterpret_cast<const float4*>(&in[buf][0][row0 + i]);
+      const float4 k4 = *reinterpret_cast<const float4*>(&in[buf][1][row0 + i]);
+      const float4 d4 = *reinterpret_cast<const float4*>(&in[buf][2][row0 + i]);
+      const float qs[4] = {q4.x, q4.y, q4.z, q4.w}, ks[4] = {k4.x, k4.y, k4.z, k4.w}, ds[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float sd = S[i + e] * ds[e];
+        S[i + e] = sd;
+        kreg[i + e] = ks[e];
+        pk = fmaf(sd, ks[e], pk);
+        pq = fmaf(sd, qs[e], pq);
+        kq = fmaf(ks[e], qs[e], kq);
       }
     }
-    float* rd = red + (size_t)(tok & 1) * 4 * 65;
+    float* rd = &red[tok & 1][0][0];
     rd[warp * 65 + lane] = pk;
     rd[warp * 65 + 32 + lane] = pq;
     if (lane == 0) rd[warp * 65 + 64] = kq;
     __syncthreads();
-    if (tok + 2 < n) {  // into the buffer that token tok - 1 used: every warp has left that token by now
-      float* nb = in + (size_t)((tok + 2) % 3) * 3 * dim;
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int i = threadIdx.x + e * 128;
-        if (i < dim) { nb[i] = nq[e]; nb[dim + i] = nk[e]; nb[2 * dim + i] = ng[e]; }
-      }
-    }
+    // into the buffer that token tok - 1 used: every warp has left that token by now
+    if (tok + 2 < n) put((tok + 2) % 3, nq, nk, nd);
     float sk = 0.f, sq = 0.f, skq = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
+    for (int w = 0; w < DR_WARPS; ++w) {
       sk += rd[w * 65 + lane];
       sq += rd[w * 65 + 32 + lane];
       skq += rd[w * 65 + 64];
     }
     const float u = bt * (v - sk);
 #pragma unroll
-    for (int i = 0; i < RW; ++i)
-      if (row0 + i < dim) S[i] = fmaf(b[dim + row0 + i], u, S[i]);
+    for (int i = 0; i < RW; ++i) S[i] = fmaf(kreg[i], u, S[i]);
     if (warp == 0 && live) out[t * heads * vdim + (size_t)h * vdim + col] = fmaf(skq, u, sq);
   }
   if (live) {
@@ -268,14 +272,13 @@ extern "C" int bn_delta_rule(const float* qn, const float* kn, const float* vc, 
   const int col_tiles = (vdim + 31) / 32;
   const long long blocks = (long long)n_seqs * heads * col_tiles;
   if (blocks > 2147483647LL) return BN_ERR_BAD_ARG;
-  const size_t smem = ((size_t)9 * dim + 2 * 4 * 65) * sizeof(float);
-#define DR_RUN(RW)                                                                                                       \
-  BN_LAUNCH(delta_rule_kernel<RW>, (unsigned)blocks, 128, smem, stream, qn, kn, vc, decay, beta, state, (size_t)state_stride, \
+#define DR_RUN(RW)                                                                                                      \
+  BN_LAUNCH(delta_rule_kernel<RW>, (unsigned)blocks, DR_THREADS, 0, stream, qn, kn, vc, decay, beta, state, (size_t)state_stride, \
             seq_start, slots, heads, kv_heads, dim, vdim, col_tiles, out)
-  if (dim <= 32) DR_RUN(8);
-  else if (dim <= 64) DR_RUN(16);
-  else if (dim <= 128) DR_RUN(32);
-  else DR_RUN(64);
+  if (dim <= 32) DR_RUN(4);
+  else if (dim <= 64) DR_RUN(8);
+  else if (dim <= 128) DR_RUN(16);
+  else DR_RUN(32);
 #undef DR_RUN
   return BN_OK;
 }
