@@ -60,6 +60,9 @@ class StepContext:
     # schedule entry that is running (-1 outside the layers)
     diag: Optional[object] = None
     layer: int = -1
+    # what parts worked out for this step on the host and may share (several layers of one kind ask for the same
+    # lists of positions): keyed by who made it and from which constants
+    memo: dict = field(default_factory=dict)
 
     def tap(self, tag: str, value, rows=None) -> None:
         """Show a named intermediate tensor to the diagnostics, if there are any (a part calls this

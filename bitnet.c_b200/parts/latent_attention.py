@@ -3,6 +3,7 @@ from __future__ import annotations
 
 from typing import Dict, Optional
 
+import numpy as np
 import torch
 
 from ..csrc import ops
@@ -21,7 +22,12 @@ class LatentAttention(Mixer):
     query part is carried into the latent space first (one small product per head), the scores are
     q' . [c | k_rot] with q' = [W_uk^T q_plain | q_rot], the weighted sum of the rows' first kv_rank numbers is
     the head's output in the latent space, and W_uv brings it back (another small product per head).  The
-    values are a part of the key rows, so the cache holds no value plane."""
+    values are a part of the key rows, so the cache holds no value plane.
+
+    Runs of new tokens whose key rows are too wide for the tensor-core kernel (more than 256 numbers) take the
+    other order: the rows every new token sees are read back from the cache, W_uk and W_uv make per-head keys
+    [W_uk c | k_rot] and values of them (two products over all those rows), which go into scratch pages of the
+    step, and the tensor-core kernel runs on these with the queries as projected."""
 
     kernels = ("linear", "linear_mma", "linear_tc", "gemm_tc", "attention", "attention_prefill", "rotary_pairs", "norm")
     TILED_MIN_TOKENS = 16  # runs of new tokens from this many on take the tensor-core kernel (bfloat16)
@@ -71,6 +77,7 @@ class LatentAttention(Mixer):
         # per head: W_uk as [dim, kv_rank] (plain query part -> latent space), W_uv as [vdim, kv_rank]
         self.w_uk = tensors["uk"].reshape(s.n_heads, s.head_dim, s.kv_rank).contiguous()
         self.w_uv = tensors["uv"].reshape(s.n_heads, s.v_head_dim, s.kv_rank).contiguous()
+        self.w_uk_flat, self.w_uv_flat = tensors["uk"], tensors["uv"]
 
     def cache_request(self) -> KvRequest:
         s = self.spec
@@ -90,6 +97,11 @@ class LatentAttention(Mixer):
         self.position.apply(ckv, ctx, xq=q, q_off=0, n_q_heads=H, q_head_stride=d + dr, q_rot_off=d, k_off=0, n_k_heads=1,
                             k_head_stride=row, k_rot_off=rank, k_row=row, tok_seq=ctx.tok_seq, slots=ctx.slots,
                             page_table=kv.page_table, k_cache=kv.k)
+        gate = ckv[:, self.g_off:] if s.head_gate else None
+        tiled = dt == torch.bfloat16 and not ctx.decode and ctx.tile_seq is not None and ctx.max_new >= self.TILED_MIN_TOKENS
+        if (tiled and (row > 256 or row % 16 or rank % 16) and (d + dr) % 16 == 0 and s.v_head_dim % 16 == 0 and d + dr <= 256
+                and s.v_head_dim <= 256 and ctx.host_new):
+            return self._per_head_keys(q, gate, ctx, kv)
         # queries in the latent space: [W_uk^T q_plain | q_rot] per head
         q3 = q.view(n, H, d + dr)
         ql = torch.empty((n, H, row), dtype=q.dtype, device=q.device)
@@ -98,9 +110,7 @@ class LatentAttention(Mixer):
         if ctx.diag is not None:
             ctx.tap("attn_q", lambda: ql.view(n, H * row))
         out = torch.empty((n, H * rank), dtype=dt, device=h.device)
-        gate = ckv[:, self.g_off:] if s.head_gate else None
-        if (dt == torch.bfloat16 and not ctx.decode and ctx.tile_seq is not None and ctx.max_new >= self.TILED_MIN_TOKENS
-                and row % 16 == 0 and rank % 16 == 0 and row <= 256):
+        if tiled and row % 16 == 0 and rank % 16 == 0 and row <= 256:
             # runs of new tokens: 64 tokens of a sequence and a head per block on the tensor cores, the
             # softmax weights with 16 bits of mantissa
             ops.attention_prefill(ql, H * row, out, H, 1, row, s.scale, s.window, ctx.tile_seq, ctx.tile_row0, ctx.seq_start,
@@ -114,3 +124,50 @@ class LatentAttention(Mixer):
         # back from the latent space: W_uv per head, heads side by side
         o = torch.bmm(out.view(n, H, rank).transpose(0, 1), self.w_uv.to(dt).transpose(1, 2)).transpose(0, 1).contiguous()
         return ops.linear(o.view(n, H * s.v_head_dim), self.w_o, out_dtype=torch.float32)
+
+    def _seen_rows(self, ctx, device):
+        """For this step: which cached positions its new tokens see (sequence and position of each, on the device),
+        and a page table of scratch pages that holds just those, by sequence of the step and page index within the
+        sequence.  The same for every layer of one window, so it is made once per step."""
+        key = ("latent_attention.seen", self.spec.window)
+        if key not in ctx.memo:
+            w = self.spec.window
+            seq, pos, spans = [], [], []
+            for i, (p0, n) in enumerate(zip(ctx.host_pos0, ctx.host_new)):
+                lo = max(0, p0 - w + 1) if w > 0 else 0
+                seq.append(np.full(p0 + n - lo, i, dtype=np.int64))
+                pos.append(np.arange(lo, p0 + n, dtype=np.int64))
+                spans.append((lo // ops.PAGE, (p0 + n - 1) // ops.PAGE))
+            table = np.zeros((len(spans), max(b for _a, b in spans) + 1), dtype=np.int32)
+            at = 0
+            for i, (a, b) in enumerate(spans):
+                table[i, a:b + 1] = np.arange(at, at + b - a + 1)
+                at += b - a + 1
+            both = torch.from_numpy(np.stack([np.concatenate(seq), np.concatenate(pos)])).pin_memory().to(device, non_blocking=True)
+            ctx.memo[key] = (both[0], both[1], torch.from_numpy(table).pin_memory().to(device, non_blocking=True), at,
+                             torch.arange(len(spans), dtype=torch.int32, device=device))
+        return ctx.memo[key]
+
+    def _per_head_keys(self, q, gate, ctx, kv):
+        s = self.spec
+        H, d, dr, dv, rank = s.n_heads, s.head_dim, s.rot_dim, s.v_head_dim, s.kv_rank
+        dt, dev = self.build.dtype, q.device
+        seq, pos, table, n_pages, rows_of = self._seen_rows(ctx, dev)
+        page, r = pos // ops.PAGE, pos % ops.PAGE
+        rows = kv.k[kv.page_table[ctx.slots[seq].long(), page].long(), 0, r]  # [seen, latent | rotated key part]
+        c = rows[:, :rank].contiguous()
+        keys = torch.empty((rows.shape[0], H, d + dr), dtype=dt, device=dev)
+        keys[:, :, :d] = ops.linear(c, self.w_uk_flat, out_dtype=dt).view(-1, H, d)
+        keys[:, :, d:] = rows[:, None, rank:]
+        values = ops.linear(c, self.w_uv_flat, out_dtype=dt).view(-1, H, dv)
+        # scratch pages start as zeros: rows of a page that no position fills are masked, and zero times them is zero
+        k_s = torch.zeros((n_pages, H, ops.PAGE, d + dr), dtype=dt, device=dev)
+        v_s = torch.zeros((n_pages, H, ops.PAGE, dv), dtype=dt, device=dev)
+        to = table[seq, page].long()
+        k_s[to, :, r] = keys
+        v_s[to, :, r] = values
+        out = torch.empty((q.shape[0], H * dv), dtype=dt, device=dev)
+        ops.attention_prefill(q, H * (d + dr), out, H, H, d + dr, s.scale, s.window, ctx.tile_seq, ctx.tile_row0, ctx.seq_start,
+                              ctx.seq_pos0, rows_of, table, k_s, v_s, gate=gate, gate_stride=self.row, precise=True)
+        ctx.tap("attn_out", out)
+        return ops.linear(out, self.w_o, out_dtype=torch.float32)

@@ -83,7 +83,24 @@ CASE_C = {
 }
 LOW_RANKS_C = {2: (16, 16)}
 
-CASES = {"A": (CASE_A, LOW_RANKS_A), "B": (CASE_B, LOW_RANKS_B), "C": (CASE_C, LOW_RANKS_C)}
+# latents wider than the tensor-core kernel's key rows: runs of new tokens in bfloat16 take per-head keys and values
+# made from the cached rows; with and without a window, behind cached tokens and from the first token on
+CASE_D = {
+    "architecture": "Lotilix", "vocab": 120, "width": 64, "norm": {"eps": 1e-6}, "token_side": {"dim": 16},
+    "layers": [
+        {"type": "latent_attention", "mixer": {"heads": 2, "dim": 16, "rot_dim": 16, "vdim": 32, "q_rank": 24, "kv_rank": 272,
+                                               "scale": 0.8, "rot": {"base": 300.0, "dims": 16}, "mask": {"size": 40}},
+         "mlp": {"kind": "dense", "ff": 32}},
+        {"type": "latent_attention", "mixer": {"heads": 3, "dim": 32, "rot_dim": 16, "vdim": 16, "q_rank": 32, "kv_rank": 304,
+                                               "scale": 0.6, "rot": {"base": 1e4, "dims": 16}},
+         "mlp": None},
+        {"type": "latent_attention", "mixer": {"heads": 2, "dim": 16, "rot_dim": 16, "vdim": 32, "q_rank": 24, "kv_rank": 272,
+                                               "scale": 0.8, "rot": {"base": 300.0, "dims": 16}, "mask": {"size": 40}},
+         "mlp": {"kind": "dense", "ff": 32}},
+    ],
+}
+
+CASES = {"A": (CASE_A, LOW_RANKS_A), "B": (CASE_B, LOW_RANKS_B), "C": (CASE_C, LOW_RANKS_C), "D": (CASE_D, {})}
 
 
 def tensor_shapes(cfg: dict, low_ranks: dict) -> dict:

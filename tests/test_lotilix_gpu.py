@@ -319,7 +319,7 @@ def _poison(cache):
         s.fill_(float("nan"))
 
 
-@pytest.mark.parametrize("case", ["A", "B", "C"])
+@pytest.mark.parametrize("case", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_models_step_like_the_plain_statement_however_the_tokens_are_cut(folders, cuda_device, case, dtype):
     cfg = lc.CASES[case][0]

@@ -72,7 +72,7 @@ def test_delta_rule_writes_before_it_reads_and_forgets_by_channel():
     assert np.allclose(o[1], S1.T @ q[1])
 
 
-@pytest.mark.parametrize("case", ["A", "B", "C"])
+@pytest.mark.parametrize("case", ["A", "B", "C", "D"])
 def test_faults_in_the_mechanisms_move_the_logits_of_the_test_models(case):
     """The models of the engine tests are sharp enough: each of these faults moves some logit by far more than
     the engine's float32 tolerance, so a test that passes excludes them."""
