@@ -102,9 +102,10 @@ __global__ void delta_tail_kernel(const T* __restrict__ proj, int stride, int q_
 
 // The recurrence, token by token.  A block of eight warps per (sequence, head, 32 value columns): a lane
 // holds its column of S in registers, a warp an eighth of the rows (RW each, a multiple of 4); the tokens' q, k
-// and decay rows pass through shared memory three tokens deep (rows past dim are zeros, so that the state rows
+// and decay rows pass through shared memory four tokens deep (rows past dim are zeros, so that the state rows
 // there stay zero and the loops need no bounds), read four numbers at a time, and one barrier per token is
-// enough.  Since o = (gS)^T q + (k . q) u, both read-outs of the decayed state are taken in one pass over the rows.
+// enough.  What a token needs from memory is asked for three tokens ahead and rests in registers for one token
+// before it is put down, so that no load is waited for.  Since o = (gS)^T q + (k . q) u, both read-outs of the decayed state are taken in one pass over the rows.
 #define DR_WARPS 8
 #define DR_THREADS (DR_WARPS * 32)
 template <int RW>
@@ -117,7 +118,7 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const float* __r
   pdl_launch_dependents();
   pdl_wait();
   constexpr int ROWS = DR_WARPS * RW;    // rows of the padded state, >= dim
-  __shared__ __align__(16) float in[3][3][ROWS];       // [token % 3][q, k, decay][row]
+  __shared__ __align__(16) float in[4][3][ROWS];       // [token % 4][q, k, decay][row]
   __shared__ float red[2][DR_WARPS][65];               // the warps' partial read-outs and k . q
   const int tile = blockIdx.x % col_tiles, h = (blockIdx.x / col_tiles) % heads, s = blockIdx.x / (col_tiles * heads);
   const int g = h / (heads / kv_heads);
@@ -144,24 +145,29 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const float* __r
   auto put = [&](int buf, float q, float k, float d) {
     if (fetches) { in[buf][0][my_row] = q; in[buf][1][my_row] = k; in[buf][2][my_row] = d; }
   };
+  float nq = 0.f, nk = 0.f, nd = 0.f;  // the rows of token tok + 2, asked for one token ago, put down at the top of this one
   {
     float q, k, d;
-    if (n > 0) { fetch(0, q, k, d); put(0, q, k, d); }
-    if (n > 1) { fetch(1, q, k, d); put(1, q, k, d); }
+    if (n > 0 && fetches) { fetch(0, q, k, d); put(0, q, k, d); }
+    if (n > 1 && fetches) { fetch(1, q, k, d); put(1, q, k, d); }
+    if (n > 2 && fetches) fetch(2, nq, nk, nd);
   }
   __syncthreads();
-  float v_next = (n > 0 && live) ? vc[(size_t)start * heads * vdim + (size_t)h * vdim + col] : 0.f;
-  float b_next = n > 0 ? beta[(size_t)start * heads + h] : 0.f;
+  auto v_of = [&](int tok) { return live ? vc[(size_t)(start + tok) * heads * vdim + (size_t)h * vdim + col] : 0.f; };
+  auto b_of = [&](int tok) { return beta[(size_t)(start + tok) * heads + h]; };
+  float v0 = n > 0 ? v_of(0) : 0.f, v1 = n > 1 ? v_of(1) : 0.f, b0 = n > 0 ? b_of(0) : 0.f, b1 = n > 1 ? b_of(1) : 0.f;
   for (int tok = 0; tok < n; ++tok) {
     const size_t t = (size_t)(start + tok);
-    const int buf = tok % 3;
-    const float v = v_next, bt = b_next;
-    if (tok + 1 < n) {
-      v_next = live ? vc[(t + 1) * heads * vdim + (size_t)h * vdim + col] : 0.f;
-      b_next = beta[(t + 1) * heads + h];
+    const int buf = tok & 3;
+    const float v = v0, bt = b0;
+    v0 = v1; b0 = b1;
+    if (tok + 2 < n) {
+      v1 = v_of(tok + 2);
+      b1 = b_of(tok + 2);
+      // into the buffer that token tok - 2 used: every warp has left that token by now (the barrier of tok - 1)
+      put((tok + 2) & 3, nq, nk, nd);
     }
-    float nq = 0.f, nk = 0.f, nd = 0.f;  // the rows of the token after next, asked for now and put down after the barrier
-    if (tok + 2 < n && fetches) fetch(tok + 2, nq, nk, nd);
+    if (tok + 3 < n && fetches) fetch(tok + 3, nq, nk, nd);
     float pk = 0.f, pq = 0.f, kq = 0.f;
     float kreg[RW];
 #pragma unroll
@@ -185,8 +191,6 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const float* __r
     rd[warp * 65 + 32 + lane] = pq;
     if (lane == 0) rd[warp * 65 + 64] = kq;
     __syncthreads();
-    // into the buffer that token tok - 1 used: every warp has left that token by now
-    if (tok + 2 < n) put((tok + 2) % 3, nq, nk, nd);
     float sk = 0.f, sq = 0.f, skq = 0.f;
 #pragma unroll
     for (int w = 0; w < DR_WARPS; ++w) {
