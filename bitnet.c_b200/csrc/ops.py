@@ -1129,13 +1129,16 @@ def rotary_pairs_append(x: torch.Tensor, freqs: torch.Tensor, tok_pos: torch.Ten
                         k_rot_off: int = 0, k_row: int = 0, v_off: int = 0, v_head_stride: int = 0, v_row: int = 0,
                         tok_seq: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
                         page_table: Optional[torch.Tensor] = None, k_cache: Optional[torch.Tensor] = None,
-                        v_cache: Optional[torch.Tensor] = None) -> None:
+                        v_cache: Optional[torch.Tensor] = None, norm_len: int = 0, norm_w: Optional[torch.Tensor] = None,
+                        norm_eps: float = 0.0) -> None:
     """Rotary encoding in the interleaved pairing, in place: in every row of x the pairs (2i, 2i + 1), i < len(freqs),
     of the rotated part of each query head (heads ``q_head_stride`` apart from ``q_off``, the part at ``q_rot_off``
     inside a head) and of each key head (likewise) are turned by ``tok_pos * freqs[i]``.  With a cache the first
     ``k_row`` numbers of every key head go there after rotation, and (``v_cache``) the first ``v_row`` numbers of
     the heads at ``v_off`` as they were before it, so ``v_off`` may equal ``k_off``.  ``xq``: the tensor that holds
-    the query heads when it is not x (x then holds the key and value heads only)."""
+    the query heads when it is not x (x then holds the key and value heads only).  ``norm_len`` > 0 (one key head): the
+    key row's first ``norm_len`` numbers are first divided by their root mean square (``norm_eps`` inside the root) and
+    multiplied by ``norm_w``, in place: a latent that is cached normed, in the same launch."""
     _need(x, "x", dims=2)
     xq = x if xq is None else xq
     _need(xq, "xq", x.dtype, 2)
@@ -1161,11 +1164,16 @@ def rotary_pairs_append(x: torch.Tensor, freqs: torch.Tensor, tok_pos: torch.Ten
         pt_stride = page_table.shape[1]
     elif v_cache is not None:
         raise KernelError("rotary_pairs_append: a value cache needs a key cache")
+    if norm_len:
+        _need(norm_w, "norm_w", dims=1)
+        if norm_w.shape[0] != norm_len or n_k_heads != 1 or norm_len > k_rot_off:
+            raise KernelError("rotary_pairs_append: the normed part must be one key head's numbers in front of its rotated part")
     _check(_fn("rotary_pairs", "bn_rotary_pairs_append")(
         _ptr(xq), int(xq.shape[1]), _ptr(x), int(_code(x)), int(n), int(x.shape[1]), _ptr(freqs), int(freqs.shape[0]), _ptr(tok_pos), int(q_off),
         int(n_q_heads), int(q_head_stride), int(q_rot_off), int(k_off), int(n_k_heads), int(k_head_stride), int(k_rot_off),
         int(k_row), int(v_off), int(v_head_stride), int(v_row), _ptr(tok_seq), _ptr(slots), _ptr(page_table), int(pt_stride),
-        _ptr(k_cache), _ptr(v_cache), _stream()), "rotary_pairs_append")
+        _ptr(k_cache), _ptr(v_cache), int(norm_len), _ptr(norm_w), int(_code(norm_w)) if norm_w is not None else 0,
+        c_float(norm_eps), _stream()), "rotary_pairs_append")
 
 
 def residual_add(x: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor] = None,

@@ -8,7 +8,9 @@
 // (rot_off), so heads of the form [plain | rotated] and keys whose last numbers are a rotated part
 // shared by all heads take the same kernel.
 //
-// One block per token, three phases with a barrier between them:
+// One block per token, phases with a barrier between them:
+//   0  (optional) the first norm_len numbers of the key row divided by their root mean square, times a gain:
+//      a latent that is cached normed, with its rotated part behind it (one key head)
 //   1  value heads -> cache, as they are (they may be the key heads before rotation: v_off == k_off)
 //   2  pairs of the query heads and of the key heads rotated in place
 //   3  key heads -> cache
@@ -24,16 +26,30 @@ __global__ void rotary_pairs_append_kernel(T* xq, int q_row_stride, T* xk, int r
                                            int k_row, int v_off, int v_head_stride, int v_row,
                                            const int* __restrict__ tok_seq, const int* __restrict__ slots,
                                            const int* __restrict__ page_table, int pt_stride, T* __restrict__ k_cache,
-                                           T* __restrict__ v_cache) {
+                                           T* __restrict__ v_cache, int norm_len, const void* __restrict__ norm_w,
+                                           int norm_w_dtype, float norm_eps) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float cs[RP_MAX_HALF], sn[RP_MAX_HALF];
+  __shared__ float scratch[32];
   const int t = blockIdx.x;
   const int pos = tok_pos[t];
   T* row = xk + (size_t)t * row_stride;    // the row that holds the key (and value) heads
   T* qrow = xq + (size_t)t * q_row_stride;  // the row that holds the query heads (may be the same)
   for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * freqs[i], &sn[i], &cs[i]);
   const int* pt = k_cache ? page_table + (size_t)slots[tok_seq[t]] * pt_stride : nullptr;
+  if (norm_len > 0) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < norm_len; i += blockDim.x) {
+      const float a = to_f32<T>(row[k_off + i]);
+      ss += a * a;
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)norm_len + norm_eps);
+    for (int i = threadIdx.x; i < norm_len; i += blockDim.x)
+      row[k_off + i] = from_f32<T>(to_f32<T>(row[k_off + i]) * scale * load_as_f32(norm_w, norm_w_dtype, i));
+    __syncthreads();
+  }
   if (v_cache) {
     for (int e = threadIdx.x; e < n_k_heads * v_row; e += blockDim.x) {
       const int h = e / v_row, d = e - h * v_row;
@@ -63,14 +79,19 @@ __global__ void rotary_pairs_append_kernel(T* xq, int q_row_stride, T* xk, int r
 // q_head_stride apart, the rotated part 2 * half wide from q_rot_off inside each; key heads likewise.
 // With k_cache: head h of the keys (its first k_row numbers, after rotation) goes to the cache
 // [pages, n_k_heads, BN_PAGE, k_row]; with v_cache the first v_row numbers of the heads at v_off go,
-// unrotated, to [pages, n_k_heads, BN_PAGE, v_row].
+// unrotated, to [pages, n_k_heads, BN_PAGE, v_row].  norm_len > 0 (one key head, norm_len <= k_rot_off): the key row's
+// first norm_len numbers are RMS-normed with the gain norm_w first, in place.
 extern "C" int bn_rotary_pairs_append(void* xq, int q_row_stride, void* xk, int dtype, int n, int row_stride, const float* freqs, int half,
                                       const int* tok_pos, int q_off, int n_q_heads, int q_head_stride, int q_rot_off,
                                       int k_off, int n_k_heads, int k_head_stride, int k_rot_off, int k_row, int v_off,
                                       int v_head_stride, int v_row, const int* tok_seq, const int* slots,
                                       const int* page_table, int pt_stride, void* k_cache, void* v_cache,
+                                      int norm_len, const void* norm_w, int norm_w_dtype, float norm_eps,
                                       cudaStream_t stream) {
   if (n <= 0) return BN_OK;
+  if (norm_len < 0 || (norm_len > 0 && (!norm_w || n_k_heads != 1 || norm_len > k_rot_off || !(norm_eps > 0.f) ||
+                                        (norm_w_dtype != BN_F32 && norm_w_dtype != BN_BF16))))
+    return BN_ERR_BAD_ARG;
   if ((n_q_heads > 0 && !xq) || (n_k_heads > 0 && !xk) || !tok_pos || half < 0 || half > RP_MAX_HALF || (half > 0 && !freqs) || n_q_heads < 0 || n_k_heads < 0 ||
       (n_q_heads > 0 && (q_off < 0 || q_rot_off < 0 || q_rot_off + 2 * half > q_head_stride ||
                          q_off + n_q_heads * q_head_stride > q_row_stride)) ||
@@ -83,12 +104,13 @@ extern "C" int bn_rotary_pairs_append(void* xq, int q_row_stride, void* xk, int 
   if (dtype == BN_F32)
     BN_LAUNCH(rotary_pairs_append_kernel<float>, n, RP_THREADS, 0, stream, (float*)xq, q_row_stride, (float*)xk, row_stride, freqs, half, tok_pos, q_off,
               n_q_heads, q_head_stride, q_rot_off, k_off, n_k_heads, k_head_stride, k_rot_off, k_row, v_off, v_head_stride,
-              v_row, tok_seq, slots, page_table, pt_stride, (float*)k_cache, (float*)v_cache);
+              v_row, tok_seq, slots, page_table, pt_stride, (float*)k_cache, (float*)v_cache, norm_len, norm_w, norm_w_dtype, norm_eps);
   else if (dtype == BN_BF16)
     BN_LAUNCH(rotary_pairs_append_kernel<__nv_bfloat16>, n, RP_THREADS, 0, stream, (__nv_bfloat16*)xq, q_row_stride,
               (__nv_bfloat16*)xk, row_stride, freqs, half,
               tok_pos, q_off, n_q_heads, q_head_stride, q_rot_off, k_off, n_k_heads, k_head_stride, k_rot_off, k_row, v_off,
-              v_head_stride, v_row, tok_seq, slots, page_table, pt_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache);
+              v_head_stride, v_row, tok_seq, slots, page_table, pt_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, norm_len,
+              norm_w, norm_w_dtype, norm_eps);
   else
     return BN_ERR_BAD_ARG;
   return BN_OK;

@@ -92,11 +92,11 @@ class LatentAttention(Mixer):
         ops.rmsnorm_slices(cq, s.norm_eps, 0, s.q_rank, self.g_dq)
         q = ops.linear(cq, self.w_uq, out_dtype=dt)  # [n, H * (d + dr)]
         ckv = ops.linear(h, self.w_kv, out_dtype=dt)  # [n, latent | rotated key part | gates | padding]
-        ops.rmsnorm_slices(ckv, s.norm_eps, 0, rank, self.g_dkv)
-        # rotate the heads' rotated query parts and the shared key part; the key row [c | k_rot] goes to the cache
+        # the latent normed, the heads' rotated query parts and the shared key part rotated, the key row [c | k_rot]
+        # to the cache: one launch
         self.position.apply(ckv, ctx, xq=q, q_off=0, n_q_heads=H, q_head_stride=d + dr, q_rot_off=d, k_off=0, n_k_heads=1,
                             k_head_stride=row, k_rot_off=rank, k_row=row, tok_seq=ctx.tok_seq, slots=ctx.slots,
-                            page_table=kv.page_table, k_cache=kv.k)
+                            page_table=kv.page_table, k_cache=kv.k, norm_len=rank, norm_w=self.g_dkv, norm_eps=s.norm_eps)
         gate = ckv[:, self.g_off:] if s.head_gate else None
         tiled = dt == torch.bfloat16 and not ctx.decode and ctx.tile_seq is not None and ctx.max_new >= self.TILED_MIN_TOKENS
         if (tiled and (row > 256 or row % 16 or rank % 16) and (d + dr) % 16 == 0 and s.v_head_dim % 16 == 0 and d + dr <= 256
@@ -105,7 +105,7 @@ class LatentAttention(Mixer):
         # queries in the latent space: [W_uk^T q_plain | q_rot] per head
         q3 = q.view(n, H, d + dr)
         ql = torch.empty((n, H, row), dtype=q.dtype, device=q.device)
-        ql[:, :, :rank] = torch.bmm(q3[:, :, :d].transpose(0, 1), self.w_uk.to(q.dtype)).transpose(0, 1)
+        torch.bmm(q3[:, :, :d].transpose(0, 1), self.w_uk.to(q.dtype), out=ql[:, :, :rank].transpose(0, 1))
         ql[:, :, rank:] = q3[:, :, d:]
         if ctx.diag is not None:
             ctx.tap("attn_q", lambda: ql.view(n, H * row))
@@ -122,7 +122,8 @@ class LatentAttention(Mixer):
                                   max_keys=min(ctx.max_len, s.window) if s.window > 0 else ctx.max_len)
         ctx.tap("attn_out", out)
         # back from the latent space: W_uv per head, heads side by side
-        o = torch.bmm(out.view(n, H, rank).transpose(0, 1), self.w_uv.to(dt).transpose(1, 2)).transpose(0, 1).contiguous()
+        o = torch.empty((n, H, s.v_head_dim), dtype=dt, device=h.device)
+        torch.bmm(out.view(n, H, rank).transpose(0, 1), self.w_uv.to(dt).transpose(1, 2), out=o.transpose(0, 1))
         return ops.linear(o.view(n, H * s.v_head_dim), self.w_o, out_dtype=torch.float32)
 
     def _seen_rows(self, ctx, device):
