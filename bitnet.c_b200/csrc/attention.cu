@@ -61,7 +61,7 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
                                          float* __restrict__ part, int n_splits) {
   pdl_launch_dependents();  // the next kernel in the stream may begin its prologue
   pdl_wait();               // the kernels before this one have completed and their writes are visible
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   float* qs = sm;                    // head_dim
   float* ps = qs + head_dim;         // ATT_CHUNK scores, then probabilities
   float* scratch = ps + ATT_CHUNK;   // 32
@@ -108,8 +108,13 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
         for (int d = 0; d < head_dim; d += VN) {
           float kv[VN];
           Vec16<T>::load(krow + d, kv);
+          const float4* q4 = reinterpret_cast<const float4*>(qs + d);  // four numbers of q per read
 #pragma unroll
-          for (int e = 0; e < VN; ++e) dot = fmaf(qs[d + e], kv[e], dot);
+          for (int e = 0; e < VN / 4; ++e) {
+            const float4 a = q4[e];
+            dot = fmaf(a.x, kv[4 * e], dot); dot = fmaf(a.y, kv[4 * e + 1], dot);
+            dot = fmaf(a.z, kv[4 * e + 2], dot); dot = fmaf(a.w, kv[4 * e + 3], dot);
+          }
         }
       } else {
         for (int d = 0; d < head_dim; ++d) dot = fmaf(qs[d], to_f32<T>(krow[d]), dot);
@@ -188,6 +193,174 @@ __global__ void attention_general_kernel(const T* __restrict__ q, int q_stride, 
   }
 }
 
+// The same for R query heads of one key/value head at once (a block per token and group of R heads): every key
+// and value row is read once for the R heads instead of once per head, which is what bounds the kernel above when
+// many heads share few rows (one token per sequence, grouped or multi-query heads: the rows come from the L2 R
+// times less often).  Rows of whole 16-byte pieces only (head_dim, v_dim, v_row multiples of the piece).
+template <int R>
+__device__ __forceinline__ void block_max_sum_r(float* v, float* scratch, bool is_max) {
+  // v[R] per thread -> the block's maximum (or sum) of each, to every thread; scratch holds 32 * R floats
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int r = 0; r < R; ++r) v[r] = is_max ? warp_max(v[r]) : warp_sum(v[r]);
+  __syncthreads();
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) scratch[warp * R + r] = v[r];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float a = is_max ? -INFINITY : 0.f;
+    for (int w = 0; w < nwarp; ++w) a = is_max ? fmaxf(a, scratch[w * R + r]) : a + scratch[w * R + r];
+    v[r] = a;
+  }
+}
+
+template <typename T, int R>
+__global__ void __launch_bounds__(ATT_THREADS)
+attention_grouped_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride, int n_heads,
+                         int n_kv_heads, int head_dim, int v_dim, float scale, int window, int keep_first, int chunk,
+                         int v_row, const float* __restrict__ rel, int n_rel, const T* __restrict__ gate, int gate_stride,
+                         const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, const int* __restrict__ slots,
+                         const int* __restrict__ page_table, int pt_stride, const T* __restrict__ k_cache,
+                         const T* __restrict__ v_cache, float* __restrict__ part, int n_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float sm[];
+  float* qs = sm;                           // [R][head_dim]
+  float* ps = qs + (size_t)R * head_dim;    // [R][ATT_CHUNK] probabilities
+  float* scratch = ps + R * ATT_CHUNK;      // [32 * R]
+  float* red = scratch + 32 * R;            // [R][groups * v_dim] at the end
+  const int t = blockIdx.x, h0 = blockIdx.y * R;
+  const int kvh = h0 / (n_heads / n_kv_heads);
+  const int pos = tok_pos[t];
+  const int* pt = page_table + (size_t)slots[tok_seq[t]] * pt_stride;
+  const int lo = chunk > 0 ? (pos / chunk) * chunk : (window > 0 ? max(0, pos - window + 1) : 0);
+  const int n_first = min(keep_first, lo);
+  const int n_keys = n_first + pos - lo + 1;
+  constexpr int VN = Vec16<T>::N;
+  for (int i = threadIdx.x; i < R * head_dim; i += blockDim.x)
+    qs[i] = to_f32<T>(q[(size_t)t * q_stride + (size_t)h0 * head_dim + i]);
+  __syncthreads();
+  const int per_row = v_dim / VN, groups = ATT_THREADS / per_row;
+  const int piece = threadIdx.x % per_row, group = threadIdx.x / per_row;
+  float accv[R][VN];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int e = 0; e < VN; ++e) accv[r][e] = 0.f;
+  float m_run[R], l_run[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) { m_run[r] = -INFINITY; l_run[r] = 0.f; }
+
+  for (int base = blockIdx.z * ATT_CHUNK; base < n_keys; base += ATT_CHUNK * n_splits) {
+    const int n = min(ATT_CHUNK, n_keys - base);
+    float s[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) s[r] = -INFINITY;
+    if ((int)threadIdx.x < n) {
+      const int u = base + threadIdx.x;
+      const int p = u < n_first ? u : lo + (u - n_first);
+      const T* krow = k_cache + cache_row_offset(pt, p, n_kv_heads, kvh, head_dim);
+      float dot[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r) dot[r] = 0.f;
+#pragma unroll 8
+      for (int d = 0; d < head_dim; d += VN) {
+        float kv[VN];
+        Vec16<T>::load(krow + d, kv);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const float4* q4 = reinterpret_cast<const float4*>(qs + r * head_dim + d);  // four numbers of q per read
+#pragma unroll
+          for (int e = 0; e < VN / 4; ++e) {
+            const float4 a = q4[e];
+            dot[r] = fmaf(a.x, kv[4 * e], dot[r]); dot[r] = fmaf(a.y, kv[4 * e + 1], dot[r]);
+            dot[r] = fmaf(a.z, kv[4 * e + 2], dot[r]); dot[r] = fmaf(a.w, kv[4 * e + 3], dot[r]);
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        s[r] = dot[r] * scale;
+        if (rel) s[r] += rel[(size_t)min(pos - p, n_rel - 1) * n_heads + h0 + r];
+      }
+    }
+    float m_new[R], alpha[R], p_mine[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) m_new[r] = s[r];
+    block_max_sum_r<R>(m_new, scratch, true);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      m_new[r] = fmaxf(m_run[r], m_new[r]);
+      alpha[r] = (m_run[r] == -INFINITY) ? 0.f : expf(m_run[r] - m_new[r]);
+      p_mine[r] = ((int)threadIdx.x < n) ? expf(s[r] - m_new[r]) : 0.f;
+      ps[r * ATT_CHUNK + threadIdx.x] = p_mine[r];
+    }
+    block_max_sum_r<R>(p_mine, scratch, false);  // has the barriers that publish ps[]
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      l_run[r] = l_run[r] * alpha[r] + p_mine[r];
+      m_run[r] = m_new[r];
+#pragma unroll
+      for (int e = 0; e < VN; ++e) accv[r][e] *= alpha[r];
+    }
+    if (group < groups) {
+      // eight rows of values in flight at a time: a row alone leaves the thread waiting for its one load
+      constexpr int VB = 8;
+      for (int j0 = group; j0 < n; j0 += VB * groups) {
+        float vv[VB][VN];
+#pragma unroll
+        for (int b = 0; b < VB; ++b) {
+          const int j = j0 + b * groups;
+          if (j < n) {
+            const int u = base + j;
+            const int p = u < n_first ? u : lo + (u - n_first);
+            Vec16<T>::load(v_cache + cache_row_offset(pt, p, n_kv_heads, kvh, v_row) + piece * VN, vv[b]);
+          }
+        }
+#pragma unroll
+        for (int b = 0; b < VB; ++b) {
+          const int j = j0 + b * groups;
+          if (j < n) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+              const float w = ps[r * ATT_CHUNK + j];
+#pragma unroll
+              for (int e = 0; e < VN; ++e) accv[r][e] = fmaf(w, vv[b][e], accv[r][e]);
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();  // ps[] is rewritten by the next chunk
+  }
+  // the groups' sums meet in shared memory: red[r][group][v_dim]
+  if (group < groups) {
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int e = 0; e < VN; ++e) red[((size_t)r * groups + group) * v_dim + piece * VN + e] = accv[r][e];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int h = h0 + r;
+    float inv = 1.0f / l_run[r];
+    if (gate) inv *= 1.0f / (1.0f + expf(-to_f32<T>(gate[(size_t)t * gate_stride + h])));
+    T* orow = out + (size_t)t * out_stride + (size_t)h * v_dim;
+    float* prow = part ? part + (((size_t)t * n_heads + h) * n_splits + blockIdx.z) * (v_dim + 2) : nullptr;
+    if (prow && threadIdx.x == 0) { prow[0] = m_run[r]; prow[1] = l_run[r]; }
+    for (int d = threadIdx.x; d < v_dim; d += ATT_THREADS) {
+      float a = 0.f;
+      for (int g = 0; g < groups; ++g) a += red[((size_t)r * groups + g) * v_dim + d];
+      if (prow) prow[2 + d] = a;
+      else orow[d] = from_f32<T>(a * inv);
+    }
+  }
+}
+
 // out[t][h] = sum_z e^{m_z - M} acc_z / sum_z e^{m_z - M} l_z (times the logistic function of the gate), M = max_z m_z
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part, int n_splits, int n_heads, int v_dim,
@@ -236,6 +409,44 @@ extern "C" int bn_attention_general_ex(const void* q, int q_stride, void* out, i
       (!wide && v_dim > 8 * ATT_THREADS) || (rel && n_rel <= 0))
     return BN_ERR_BAD_ARG;
   if (n_heads > 65535) return BN_ERR_BAD_ARG;
+  // few tokens whose heads share rows: the heads of a key/value head four (or two) at a time, rows read once for them
+  const int gq = n_heads / n_kv_heads;
+  const int R = (gq % 4 == 0) ? 4 : ((gq % 2 == 0) ? 2 : 1);
+  if (R > 1 && wide && head_dim % vn == 0 && n_tokens <= 256) {
+    dim3 ggrid(n_tokens, n_heads / R, n_splits);
+    const size_t gsmem = ((size_t)R * head_dim + R * ATT_CHUNK + 32 * R + (size_t)R * ATT_THREADS * vn) * sizeof(float);
+#define BN_GROUPED(TT, RR)                                                                                                  \
+  do {                                                                                                                      \
+    if (gsmem > 48 * 1024) {                                                                                                \
+      static size_t granted = 0;                                                                                            \
+      if (gsmem > granted) {                                                                                                \
+        cudaError_t e = cudaFuncSetAttribute(attention_grouped_kernel<TT, RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gsmem); \
+        if (e != cudaSuccess) return BN_ERR_LAUNCH + (int)e;                                                                \
+        granted = gsmem;                                                                                                    \
+      }                                                                                                                     \
+    }                                                                                                                       \
+    BN_LAUNCH((attention_grouped_kernel<TT, RR>), ggrid, ATT_THREADS, gsmem, stream, (const TT*)q, q_stride, (TT*)out,       \
+              out_stride, n_heads, n_kv_heads, head_dim, v_dim, scale, window, keep_first, chunk, v_row, rel, n_rel,        \
+              (const TT*)gate, gate_stride, tok_seq, tok_pos, slots, page_table, pt_stride, (const TT*)k_cache,              \
+              (const TT*)v_cache, part, n_splits);                                                                          \
+  } while (0)
+    if (gsmem <= 160 * 1024 && (dtype == BN_F32 || dtype == BN_BF16)) {
+      if (dtype == BN_F32) { if (R == 4) BN_GROUPED(float, 4); else BN_GROUPED(float, 2); }
+      else { if (R == 4) BN_GROUPED(__nv_bfloat16, 4); else BN_GROUPED(__nv_bfloat16, 2); }
+#undef BN_GROUPED
+      if (part) {
+        dim3 mgrid(n_tokens, n_heads);
+        if (dtype == BN_F32)
+          BN_LAUNCH((attention_merge_kernel<float>), mgrid, 128, 0, stream, (const float*)part, n_splits, n_heads, v_dim,
+                    (const float*)gate, gate_stride, (float*)out, out_stride);
+        else
+          BN_LAUNCH((attention_merge_kernel<__nv_bfloat16>), mgrid, 128, 0, stream, (const float*)part, n_splits, n_heads, v_dim,
+                    (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, out_stride);
+      }
+      BN_CHECK_LAUNCH();
+      return BN_OK;
+    }
+  }
   dim3 grid(n_tokens, n_heads, n_splits);
   size_t smem = (head_dim + ATT_CHUNK + 32 + ATT_THREADS * 8) * sizeof(float);  // q, scores, reduction scratch, the groups' sums
   if (dtype == BN_F32)

@@ -368,8 +368,16 @@ def attention_general(q: torch.Tensor, q_stride: int, out: torch.Tensor, n_token
         if not gate.is_cuda or gate.dtype != q.dtype or gate.stride(-1) != 1 or gate.shape[-1] < n_heads or gate_stride <= 0:
             raise KernelError("attention: gate must be a CUDA view of q's type with unit inner stride and one number per head")
     splits = 1
-    if max_keys > 2 * DECODE_CHUNK and n_tokens * n_heads < 2 * n_sms(q.device):
-        splits = min(16, (max_keys + DECODE_CHUNK - 1) // DECODE_CHUNK, max(1, 4 * n_sms(q.device) // (n_tokens * n_heads)))
+    # blocks per split: one per token and head, or per token and group of heads where the kernel takes the heads of a
+    # key/value head four or two at a time (few tokens, rows of whole 16-byte pieces)
+    per_block = 1
+    piece = 4 if q.dtype == torch.float32 else 8
+    if n_tokens <= 256 and head_dim % piece == 0 and v_dim % piece == 0 and (v_row or v_dim) % piece == 0 and v_dim // piece <= 128:
+        gq = n_heads // n_kv_heads
+        per_block = 4 if gq % 4 == 0 else (2 if gq % 2 == 0 else 1)
+    blocks = n_tokens * n_heads // per_block
+    if max_keys > 2 * DECODE_CHUNK and blocks < 2 * n_sms(q.device):
+        splits = min(16, (max_keys + DECODE_CHUNK - 1) // DECODE_CHUNK, max(1, 4 * n_sms(q.device) // blocks))
     if (keep_first or rel is not None or gate is not None or v_dim != head_dim or splits > 1 or chunk or v_row):
         part = None
         if splits > 1:

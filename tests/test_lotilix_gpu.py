@@ -164,15 +164,17 @@ def _plain_attention(q, keys, values, pos, scale, rule, size, gate=None):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("mask,size", [("chunk", 50), ("chunk", 64), ("chunk", 7), ("window", 37), ("window", 64), ("none", 0)])
-def test_attention_at_the_edges_of_chunks_and_windows_with_one_key_that_stands_out(cuda_device, dtype, mask, size):
+@pytest.mark.parametrize("H,G", [(4, 2), (8, 2), (3, 1)])
+def test_attention_at_the_edges_of_chunks_and_windows_with_one_key_that_stands_out(cuda_device, dtype, mask, size, H, G):
     """Among some hundred keys the one just outside the mask gets a score far above all others, and so does,
     in a second run, the one just inside: the first must not show in the result, the second must own it.
     Both kernels (any mix of tokens; runs of new tokens on the tensor cores), values inside the key rows or in
-    a plane of their own, single tokens and runs that cross the edges."""
+    a plane of their own, single tokens and runs that cross the edges; two, four and three query heads on a
+    key/value head (the general kernel takes them two or four at a time, or one by one)."""
     from bitnet_c_b200.csrc import ops
     t = DT[dtype]
     rng = np.random.default_rng(size + len(mask))
-    H, G, d, dv = 4, 2, 32, 16
+    d, dv = 32, 16
     rule = {"chunk": pl.sees_chunk, "window": pl.sees_window, "none": pl.sees_window}[mask]
     lens, new = [200, 131, 64], [1, 70, 64]
     T = sum(new)
