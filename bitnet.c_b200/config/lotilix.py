@@ -136,7 +136,7 @@ class LotilixConfig:
             heads, kv_heads, dim = _int(m, "heads", where), _int(m, "kv_heads", where), _int(m, "dim", where)
             if heads % kv_heads:
                 raise ConfigError(f"config.json: {where}: {heads} heads are not a multiple of {kv_heads} kv_heads")
-            if _int(m, "vdim", where) != dim:
+            if m.get("vdim") is not None and _int(m, "vdim", where) != dim:
                 raise ConfigError(f"config.json: {where}: the values are the keys, so vdim={m['vdim']} must equal dim={dim}")
             return BiasAttentionSpec(
                 width=self.width, n_heads=heads, n_kv_heads=kv_heads, head_dim=dim, v_head_dim=dim, scale=_num(m, "scale", where),
