@@ -381,6 +381,47 @@ def test_a_long_prompt_and_long_decoding_far_past_every_mask(folders, cuda_devic
     assert held == 0 or all(not h for g in cache.groups for h in g.held.values())
 
 
+ONE_KIND = {
+    "delta": [{"type": "channel_delta", "mixer": {"heads": 3, "kv_heads": 1, "dim": 24, "vdim": 40, "conv": 4},
+               "mlp": {"kind": "dense", "ff": 96}}] * 3,
+    "latent": [{"type": "latent_attention", "mixer": {"heads": 5, "dim": 24, "rot_dim": 8, "vdim": 16, "q_rank": 40, "kv_rank": 72,
+                                                      "scale": 0.3, "rot": {"base": 1e4, "dims": 8}, "mask": {"size": 1}},
+                "mlp": None}] * 2,
+    "attention": [{"type": "attention", "mixer": {"heads": 6, "kv_heads": 3, "dim": 16, "vdim": 16, "scale": 0.5,
+                                                  "rot": {"base": 1e4, "dims": 16}, "mask": {"size": 1}},
+                   "mlp": {"kind": "dense", "ff": 96}},
+                  {"type": "attention", "mixer": {"heads": 6, "kv_heads": 6, "dim": 16, "vdim": 16, "scale": 0.5,
+                                                  "rot": {"base": 1e4, "dims": 2}, "mask": {"size": 100000}},
+                   "mlp": {"kind": "dense", "ff": 96}}],
+}
+
+
+@pytest.mark.parametrize("kind", sorted(ONE_KIND))
+@pytest.mark.parametrize("side", [True, False])
+def test_models_of_one_kind_of_mixer_only(tmp_path, cuda_device, kind, side):
+    """No key/value planes at all, or no per-sequence state at all; masks of one position and of more than any
+    prompt; the value width of the chunked mixer left out of the configuration; with and without the side input."""
+    import copy
+    cfg = {"architecture": "Lotilix", "vocab": 300, "width": 64, "norm": {"eps": 1e-5}, "layers": copy.deepcopy(ONE_KIND[kind])}
+    if side:
+        cfg["token_side"] = {"dim": 16}
+    ranks = {i: (5, 9) for i, l in enumerate(cfg["layers"]) if l["type"] == "channel_delta"}
+    w = lc.draw_weights(cfg, ranks, seed=3)
+    if kind == "attention":
+        cfg["layers"][1]["mixer"].pop("vdim")
+    folder = lc.write_folder(str(tmp_path / "m"), cfg, w)
+    reqs = {"a": random_tokens(1, 150, 300), "b": random_tokens(2, 70, 300), "c": random_tokens(3, 1, 300)}
+    plain = {r: pl.forward(cfg, w, t) for r, t in reqs.items()}
+    for dtype in ("float32", "bfloat16"):
+        model = bn.load_model(folder, dtype=dtype)
+        cache = model.new_cache(max_tokens=64 * 8, max_seqs=3)
+        _poison(cache)
+        for what, steps in (("whole", trace_whole(reqs)), ("last 30 one by one", trace_tail(reqs, 30)),
+                            ("an unequal batch", trace_batches([{"a": (reqs["a"], 20), "b": (reqs["b"], 30), "c": (reqs["c"], 0)}]))):
+            _check(replay(model, cache, steps), cfg, w, reqs, plain, dtype, f"{kind} only, {what}, {dtype}", rough_ok=True)
+        model.check_kernels()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_through_the_entry_point_and_the_replay_program(folders, cuda_device, tmp_path, dtype):
     cfg = lc.CASES["A"][0]
